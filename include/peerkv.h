@@ -1,0 +1,201 @@
+/* peerkv.h -- C ABI of the B200 peer-parallel split-K decode-attention library.
+ *
+ * Plain pointers, sizes and an opaque stream handle; no torch or C++ types.
+ * Every entry point returns 0 on success and a negative PKV_E* code otherwise;
+ * pkv_last_error() gives the message of the calling thread's last failure.
+ * Device-side trouble (a wait that ran out, a block-table id outside the pool)
+ * never traps: it is recorded in a status word that pkv_shard_status() /
+ * pkv_exchange_status() read back.
+ *
+ * The library replaces, in the PeerKV project:
+ *   - the pybind module of csrc/peer_fused_attn_ext.cu:139-145 and its host
+ *     orchestration (:37-137), JIT-loaded by umallm/peerkv/fused_attn.py:32-46;
+ *   - the kernels of csrc/peer_attn_kernels.cuh (attn_split_gqa :14-47,
+ *     attn_combine :50-61, merge2_h :64-73);
+ *   - the per-sequence gather loop of umallm/peerkv/paged.py:48-97 (the kernels
+ *     read the paged pool through the block table directly).
+ * All pointers are device pointers on the device of the object they are passed
+ * to unless a comment says otherwise.  The caller owns q, the KV pool, block
+ * tables and outputs; the library owns only the scratch inside its objects.
+ */
+#ifndef PEERKV_H_
+#define PEERKV_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PKV_ABI_VERSION 1
+
+/* return codes */
+#define PKV_OK            0
+#define PKV_E_INVALID    -1   /* bad argument (message says which) */
+#define PKV_E_CUDA       -2   /* a CUDA runtime / driver call failed */
+#define PKV_E_UNSUPPORTED -3  /* shape outside what the kernels cover */
+#define PKV_E_STATE      -4   /* object not ready (e.g. peer not attached) */
+
+/* element types */
+#define PKV_F16      0
+#define PKV_BF16     1
+#define PKV_INT8     2   /* codes; one fp16 scale per (token, kv-head) row */
+#define PKV_FP8_E4M3 3   /* e4m3fn codes; same scales */
+#define PKV_F32      4
+
+/* device status bits (OR-ed; 0 = healthy) */
+#define PKV_ST_PIPE_TIMEOUT   0x1u  /* an on-chip copy barrier was not completed in time */
+#define PKV_ST_BAD_PAGE       0x2u  /* block-table entry outside [0, n_pages) was skipped */
+#define PKV_ST_Q_TIMEOUT      0x4u  /* the query for this epoch never arrived */
+#define PKV_ST_PARTIAL_TIMEOUT 0x8u /* a peer's partial for this epoch never arrived */
+
+typedef struct pkv_shard pkv_shard;       /* one GPU's attention context */
+typedef struct pkv_exchange pkv_exchange; /* one GPU's mailboxes for q and partials */
+
+/* A KV pool as the kernels see it.  Address of element (page, tok, head, d) is
+ *   base + page*page_stride + tok*token_stride + head*head_stride + d   (elements).
+ * vLLM's [2, nb, bs, Hkv, D] cache is k = cache[0], v = cache[1], page_stride =
+ * bs*Hkv*D, token_stride = Hkv*D, head_stride = D.  The reference op's
+ * contiguous [Hkv, T, D] shard (csrc/peer_fused_attn_ext.cu:8-16) is one page of
+ * T tokens: page_size = T, token_stride = D, head_stride = T*D.
+ * Strides must be multiples of 8 elements (16 bytes for 1-byte codes), bases
+ * 16-byte aligned, head_dim 128.  k_scale / v_scale ([page][tok][head] fp16,
+ * dense) are NULL unless dtype is PKV_INT8 or PKV_FP8_E4M3. */
+typedef struct pkv_kv_view {
+  const void* k;
+  const void* v;
+  const void* k_scale;
+  const void* v_scale;
+  int32_t dtype;
+  int32_t n_kv_heads;
+  int32_t head_dim;
+  int32_t page_size;
+  int64_t n_pages;
+  int64_t page_stride;
+  int64_t token_stride;
+  int64_t head_stride;
+} pkv_kv_view;
+
+/* One decode step over ONE shard: a single query token per sequence.
+ *   q            [batch, n_q_heads, head_dim], q_dtype PKV_F16 or PKV_BF16
+ *   block_table  [batch, block_table_stride] int32 page ids of THIS pool, in
+ *                sequence order; NULL means page j of sequence b is b*block_table_stride + j
+ *   seq_lens     [batch] int32 tokens of each sequence that live in THIS shard
+ *                (0 allowed; only a sequence's last listed page may be partial)
+ *   scale        softmax scale (the reference default is 1/sqrt(head_dim)) */
+typedef struct pkv_decode_args {
+  const void* q;
+  int32_t q_dtype;
+  int32_t batch;
+  int32_t n_q_heads;
+  int32_t reserved0;
+  pkv_kv_view kv;
+  const int32_t* block_table;
+  int64_t block_table_stride;
+  const int32_t* seq_lens;
+  float scale;
+  int32_t reserved1;
+} pkv_decode_args;
+
+const char* pkv_last_error(void);
+int pkv_abi_version(void);
+
+/* ---- one GPU ------------------------------------------------------------ */
+
+/* Allocates the split-K scratch of one GPU once (no allocation per call; the
+ * reference allocates 6-14 tensors per call, csrc/peer_fused_attn_ext.cu:56-92). */
+int pkv_shard_create(pkv_shard** out, int device, int max_batch, int n_q_heads);
+int pkv_shard_destroy(pkv_shard* s);
+/* Reads (and clears) the device status word; synchronises `stream` first. */
+int pkv_shard_status(pkv_shard* s, void* stream, uint32_t* status_out);
+
+/* Shard partial in the reference's (O, lse) convention
+ * (umallm/peer_parallel_attn.py:46-71): o_part [batch, n_q_heads, 128] fp32,
+ * normalised; lse_part [batch, n_q_heads] fp32, natural log; an empty shard
+ * gives O = 0 and lse = -inf.  o_part / lse_part may point into a peer GPU's
+ * memory (P2P mapped): that is how a peer hands its partial to the home GPU. */
+int pkv_decode_partial(pkv_shard* s, const pkv_decode_args* a, float* o_part,
+                       float* lse_part, void* stream);
+
+/* Whole attention on one GPU: out [batch, n_q_heads, 128] in out_dtype
+ * (PKV_F16 / PKV_BF16 / PKV_F32); lse_out may be NULL.  Replaces the Tp == 0
+ * path of peer_fused_attn (csrc/peer_fused_attn_ext.cu:66-74). */
+int pkv_decode(pkv_shard* s, const pkv_decode_args* a, void* out, int32_t out_dtype,
+               float* lse_out, void* stream);
+
+/* Single-pass N-way LSE merge (replaces merge2_h, csrc/peer_attn_kernels.cuh:64-73,
+ * and the fold of umallm/peer_parallel_attn.py:169-172).  Part i is at
+ * o_parts + i*o_part_stride (floats), lse_parts + i*lse_part_stride; rows =
+ * batch*n_q_heads.  lse_out may be NULL. */
+int pkv_merge_partials(int device, const float* o_parts, int64_t o_part_stride,
+                       const float* lse_parts, int64_t lse_part_stride, int32_t n_parts,
+                       int32_t rows, int32_t head_dim, void* out, int32_t out_dtype,
+                       float* lse_out, void* stream);
+
+/* Per-(token, kv-head) absmax quantiser; rows = tokens*kv_heads rows of 128
+ * values in src_dtype (PKV_F16 / PKV_BF16), codes [rows, 128] 1 byte each,
+ * scales [rows] fp16.  fmt PKV_INT8 or PKV_FP8_E4M3.  No counterpart in the
+ * reference (its umallm/compression.py is a 4-bit group quantiser). */
+int pkv_quantize_kv(int device, const void* src, int32_t src_dtype, int64_t rows,
+                    void* codes, void* scales, int32_t fmt, void* stream);
+
+/* Splits a global block table into one local table per GPU, on the device, with no
+ * host round trip (replaces the .item() loop of umallm/peerkv/paged.py:52-61).
+ *   mode 0: ids in [bases[d], bases[d+1]) live on GPU d at local id gid - bases[d]
+ *           (the reference's peer_base rule is n_dev = 2, bases = {0, peer_base});
+ *   mode 1: id gid lives on GPU gid mod n_dev at local id gid div n_dev (bases unused).
+ * block_table [batch, block_table_stride] int32 and seq_lens [batch] int32 are on
+ * `device`; out_tables[d] ([batch, out_stride] int32) and out_lens[d] ([batch] int32)
+ * are host arrays of n_dev device pointers that may point into other GPUs' memory
+ * (P2P mapped).  Sequence order is kept, so only a GPU's last listed page of a
+ * sequence can be partial. */
+int pkv_split_block_table(int device, const int32_t* block_table, int64_t block_table_stride,
+                          const int32_t* seq_lens, int32_t batch, int32_t page_size,
+                          int32_t n_dev, int32_t mode, const int64_t* bases,
+                          int32_t* const* out_tables, int64_t out_stride,
+                          int32_t* const* out_lens, void* stream);
+
+/* ---- several GPUs ------------------------------------------------------- */
+
+/* Mailboxes of one GPU, allocated once: a q inbox, `world` partial slots
+ * ([max_batch, n_q_heads, 128] fp32 O + [max_batch, n_q_heads] lse each) and
+ * epoch flags.  rank 0..world-1; the home rank is the one that owns q and runs
+ * the merge.  Replaces the per-call stream/event/scratch set-up of
+ * csrc/peer_fused_attn_ext.cu:81-97 and its cudaMemcpyAsync hops (:100-101,120-123). */
+int pkv_exchange_create(pkv_exchange** out, int device, int rank, int world,
+                        int max_batch, int n_q_heads);
+int pkv_exchange_destroy(pkv_exchange* x);
+/* 64-byte inter-process handle of this GPU's mailbox slab (other process opens it). */
+int pkv_exchange_export(pkv_exchange* x, void* handle64);
+/* Map peer `peer_rank`'s slab from its exported handle (one process per GPU). */
+int pkv_exchange_import(pkv_exchange* x, int peer_rank, const void* handle64);
+/* Same process, several devices: map `peer`'s slab directly (enables peer access). */
+int pkv_exchange_attach(pkv_exchange* x, int peer_rank, pkv_exchange* peer);
+int pkv_exchange_status(pkv_exchange* x, void* stream, uint32_t* status_out);
+/* Current epoch (number of steps begun). */
+int pkv_exchange_epoch(pkv_exchange* x, uint64_t* epoch_out);
+
+/* Home rank, start of a step: bumps the epoch, stores q ([batch, n_q_heads, 128],
+ * 16-bit) into every attached peer's q inbox with P2P stores and releases their
+ * q flag.  Replaces the q broadcast + event fork of peer_fused_attn_ext.cu:100-102,114. */
+int pkv_home_publish_q(pkv_exchange* x, const void* q, int32_t batch, void* stream);
+/* Peer rank, one step: bumps the epoch, waits (bounded, device side) for the q of
+ * this epoch unless q_override is given, computes the shard partial and stores it
+ * into the home rank's slot for this rank, then releases the slot's flag.
+ * a->q is ignored unless q_override != 0. */
+int pkv_peer_step(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, int32_t home_rank,
+                  int32_t q_override, void* stream);
+/* Home rank: its own shard's partial into its own slot (after pkv_home_publish_q). */
+int pkv_home_partial(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, void* stream);
+/* Home rank: waits (bounded, device side) for the flags of the ranks in
+ * `wait_mask` (bit r = wait for rank r; ranks whose work is ordered before this
+ * call by stream order or events need no bit), then merges all `world` slots into
+ * out [batch, n_q_heads, 128] of out_dtype.  Replaces the event join + merge2_h of
+ * peer_fused_attn_ext.cu:128-131. */
+int pkv_home_merge(pkv_exchange* x, int32_t batch, uint32_t wait_mask, void* out,
+                   int32_t out_dtype, float* lse_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PEERKV_H_ */

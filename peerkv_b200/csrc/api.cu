@@ -1,0 +1,684 @@
+// C ABI of the library (declared in include/peerkv.h): argument checking, tensor-map
+// construction, persistent scratch and kernel launches.  No allocation, stream or
+// event creation happens on the per-step entry points.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/peerkv.h"
+#include "merge_kernel.cuh"
+
+namespace {
+
+thread_local std::string g_err;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return code;
+}
+
+#define PKV_CUDA(expr)                                                                  \
+  do {                                                                                  \
+    cudaError_t e_ = (expr);                                                            \
+    if (e_ != cudaSuccess)                                                              \
+      return fail(PKV_E_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_),   \
+                  __FILE__, __LINE__);                                                  \
+  } while (0)
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+    if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+  }
+  ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* base;
+  int32_t dtype, n_kv_heads, page_size;
+  int64_t n_pages, page_stride, token_stride, head_stride;
+  bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapEntry {
+  MapKey key;
+  CUtensorMap map;
+  uint64_t stamp;
+};
+
+bool is_16bit(int dt) { return dt == PKV_F16 || dt == PKV_BF16; }
+bool is_quant(int dt) { return dt == PKV_INT8 || dt == PKV_FP8_E4M3; }
+
+}  // namespace
+
+struct pkv_shard {
+  int device = 0;
+  int num_sms = 0;
+  int max_batch = 0;
+  int n_q_heads = 0;
+  int n_slots = 0;
+  float* part_o = nullptr;
+  float* part_ml = nullptr;
+  uint32_t* status = nullptr;       // device word
+  unsigned int* done_counter = nullptr;
+  std::vector<MapEntry> maps;
+  uint64_t stamp = 0;
+  bool attr_set = false;
+};
+
+namespace {
+
+int build_map(pkv_shard* s, const void* base, const pkv_kv_view& kv, const CUtensorMap** out) {
+  MapKey key;
+  memset(&key, 0, sizeof key);
+  key.base = base; key.dtype = kv.dtype; key.n_kv_heads = kv.n_kv_heads;
+  key.page_size = kv.page_size; key.n_pages = kv.n_pages; key.page_stride = kv.page_stride;
+  key.token_stride = kv.token_stride; key.head_stride = kv.head_stride;
+  for (auto& e : s->maps)
+    if (e.key == key) { e.stamp = ++s->stamp; *out = &e.map; return PKV_OK; }
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return fail(PKV_E_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  const uint64_t es = is_16bit(kv.dtype) ? 2 : 1;
+  const bool head_major = kv.head_stride >= kv.token_stride;
+  cuuint64_t dims[4];
+  cuuint64_t strides[3];
+  cuuint32_t box[4];
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  dims[0] = pkv::kHeadDim;
+  box[0] = static_cast<cuuint32_t>(128 / es);   // 128 bytes: one swizzle row
+  if (head_major) {
+    dims[1] = kv.page_size; dims[2] = kv.n_kv_heads;
+    strides[0] = kv.token_stride * es; strides[1] = kv.head_stride * es;
+    box[1] = pkv::kTileTok; box[2] = 1;
+  } else {
+    dims[1] = kv.n_kv_heads; dims[2] = kv.page_size;
+    strides[0] = kv.head_stride * es; strides[1] = kv.token_stride * es;
+    box[1] = 1; box[2] = pkv::kTileTok;
+  }
+  dims[3] = kv.n_pages;
+  strides[2] = kv.page_stride * es;
+  box[3] = 1;
+  CUtensorMapDataType dt = kv.dtype == PKV_BF16  ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : kv.dtype == PKV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  MapEntry e;
+  e.key = key;
+  CUresult r = enc(&e.map, dt, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(PKV_E_CUDA,
+                "cuTensorMapEncodeTiled failed (%d) for pool %p: heads %d page_size %d pages %lld "
+                "strides (page %lld, tok %lld, head %lld)",
+                (int)r, base, kv.n_kv_heads, kv.page_size, (long long)kv.n_pages,
+                (long long)kv.page_stride, (long long)kv.token_stride, (long long)kv.head_stride);
+  e.stamp = ++s->stamp;
+  if (s->maps.size() < 32) {
+    s->maps.push_back(e);
+    *out = &s->maps.back().map;
+  } else {
+    size_t victim = 0;
+    for (size_t i = 1; i < s->maps.size(); ++i)
+      if (s->maps[i].stamp < s->maps[victim].stamp) victim = i;
+    s->maps[victim] = e;
+    *out = &s->maps[victim].map;
+  }
+  return PKV_OK;
+}
+
+int check_args(const pkv_shard* s, const pkv_decode_args* a) {
+  if (!s || !a) return fail(PKV_E_INVALID, "null shard or args");
+  const pkv_kv_view& kv = a->kv;
+  if (a->batch < 0 || a->batch > s->max_batch)
+    return fail(PKV_E_INVALID, "batch %d outside [0, max_batch=%d]", a->batch, s->max_batch);
+  if (a->n_q_heads != s->n_q_heads)
+    return fail(PKV_E_INVALID, "n_q_heads %d differs from the shard's %d", a->n_q_heads,
+                s->n_q_heads);
+  if (kv.head_dim != pkv::kHeadDim)
+    return fail(PKV_E_UNSUPPORTED, "head_dim %d: the kernels require 128", kv.head_dim);
+  if (kv.n_kv_heads <= 0 || a->n_q_heads % kv.n_kv_heads)
+    return fail(PKV_E_INVALID, "n_q_heads %d is not a multiple of n_kv_heads %d", a->n_q_heads,
+                kv.n_kv_heads);
+  const int group = a->n_q_heads / kv.n_kv_heads;
+  if (group > 8)
+    return fail(PKV_E_UNSUPPORTED, "GQA group %d: at most 8 query heads per kv head", group);
+  if (!is_16bit(a->q_dtype)) return fail(PKV_E_INVALID, "q_dtype must be PKV_F16 or PKV_BF16");
+  if (is_16bit(kv.dtype)) {
+    if (kv.dtype != a->q_dtype)
+      return fail(PKV_E_INVALID, "16-bit KV (%d) and q (%d) must share a dtype", kv.dtype,
+                  a->q_dtype);
+  } else if (is_quant(kv.dtype)) {
+    return fail(PKV_E_UNSUPPORTED, "quantised KV attention is not built into this library yet");
+  } else {
+    return fail(PKV_E_INVALID, "kv dtype %d unknown", kv.dtype);
+  }
+  if (a->batch > 0) {
+    if (!a->q || !a->seq_lens) return fail(PKV_E_INVALID, "null q or seq_lens");
+    if (kv.n_pages > 0 && (!kv.k || !kv.v)) return fail(PKV_E_INVALID, "null k or v pool");
+    if (kv.page_size <= 0) return fail(PKV_E_INVALID, "page_size %d", kv.page_size);
+    const int64_t es = is_16bit(kv.dtype) ? 2 : 1;
+    const int64_t mod = 16 / es;
+    if (kv.page_stride % mod || kv.token_stride % mod || kv.head_stride % mod)
+      return fail(PKV_E_INVALID, "KV strides must be multiples of 16 bytes");
+    if ((reinterpret_cast<uintptr_t>(kv.k) | reinterpret_cast<uintptr_t>(kv.v)) & 15)
+      return fail(PKV_E_INVALID, "KV pool bases must be 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(a->q) & 3) return fail(PKV_E_INVALID, "q must be 4-byte aligned");
+  }
+  return PKV_OK;
+}
+
+struct LaunchOut {
+  void* out = nullptr;
+  int out_dtype = PKV_F32;
+  float* o_part = nullptr;
+  float* lse_part = nullptr;
+  uint64_t* done_flag = nullptr;
+  uint64_t done_epoch = 0;
+  const uint64_t* q_flag = nullptr;
+  uint64_t q_epoch = 0;
+};
+
+constexpr int kStages = 3;
+constexpr uint64_t kWaitNs = 2000000000ull;  // bound of every cross-GPU device-side wait
+
+int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, cudaStream_t st) {
+  int rc = check_args(s, a);
+  if (rc) return rc;
+  if (a->batch == 0) return PKV_OK;
+  DeviceGuard guard(s->device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", s->device);
+  using L = pkv::SmemLayout<kStages>;
+  if (!s->attr_set) {
+    PKV_CUDA(cudaFuncSetAttribute(pkv::decode_partial_kernel<true, kStages>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    PKV_CUDA(cudaFuncSetAttribute(pkv::decode_partial_kernel<false, kStages>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    s->attr_set = true;
+  }
+  const pkv_kv_view& kv = a->kv;
+  const int n_hb = (kv.n_kv_heads + pkv::kHeadsPerCta - 1) / pkv::kHeadsPerCta;
+  const int n_cta_x = s->num_sms / n_hb > 0 ? s->num_sms / n_hb : 1;
+
+  pkv::DecodeParams p;
+  memset(&p, 0, sizeof p);
+  p.q = a->q;
+  p.block_table = a->block_table;
+  p.seq_lens = a->seq_lens;
+  p.bt_stride = a->block_table_stride;
+  p.n_pages = kv.n_pages;
+  p.batch = a->batch;
+  p.n_q_heads = a->n_q_heads;
+  p.n_kv_heads = kv.n_kv_heads;
+  p.group = a->n_q_heads / kv.n_kv_heads;
+  p.page_size = kv.page_size;
+  p.tiles_per_page = (kv.page_size + pkv::kTileTok - 1) / pkv::kTileTok;
+  p.head_major = kv.head_stride >= kv.token_stride ? 1 : 0;
+  p.n_cta_x = n_cta_x;
+  p.scale_log2 = a->scale * 1.4426950408889634f;
+  p.part_o = s->part_o;
+  p.part_ml = s->part_ml;
+  p.status = s->status;
+  p.q_flag = lo.q_flag;
+  p.q_epoch = lo.q_epoch;
+  p.q_timeout_ns = kWaitNs;
+
+  if (kv.n_pages > 0) {
+    const CUtensorMap *mk = nullptr, *mv = nullptr;
+    rc = build_map(s, kv.k, kv, &mk);
+    if (rc) return rc;
+    CUtensorMap tk = *mk;   // copy: the cache may reallocate on the second insert
+    rc = build_map(s, kv.v, kv, &mv);
+    if (rc) return rc;
+    CUtensorMap tv = *mv;
+    dim3 grid(n_cta_x, n_hb), block(pkv::kThreads);
+    if (kv.dtype == PKV_BF16)
+      pkv::decode_partial_kernel<true, kStages><<<grid, block, L::kTotal, st>>>(tk, tv, p);
+    else
+      pkv::decode_partial_kernel<false, kStages><<<grid, block, L::kTotal, st>>>(tk, tv, p);
+    PKV_CUDA(cudaGetLastError());
+  }
+
+  pkv::CombineParams c;
+  memset(&c, 0, sizeof c);
+  c.seq_lens = a->seq_lens;
+  c.part_o = s->part_o;
+  c.part_ml = s->part_ml;
+  c.batch = a->batch;
+  c.n_q_heads = a->n_q_heads;
+  c.page_size = kv.page_size;
+  c.tiles_per_page = p.tiles_per_page;
+  c.n_cta_x = n_cta_x;
+  c.out = lo.out;
+  c.out_dtype = lo.out_dtype;
+  c.o_part = lo.o_part;
+  c.lse_part = lo.lse_part;
+  c.done_counter = s->done_counter;
+  c.done_flag = lo.done_flag;
+  c.done_epoch = lo.done_epoch;
+  dim3 cgrid(a->batch, (a->n_q_heads + pkv::kCombineHeads - 1) / pkv::kCombineHeads);
+  pkv::decode_combine_kernel<<<cgrid, 128 * pkv::kCombineHeads, (a->batch + 1) * sizeof(int), st>>>(c);
+  PKV_CUDA(cudaGetLastError());
+  return PKV_OK;
+}
+
+int read_status(int device, uint32_t* dev_word, cudaStream_t st, uint32_t* out) {
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", device);
+  uint32_t v = 0;
+  PKV_CUDA(cudaMemcpyAsync(&v, dev_word, sizeof v, cudaMemcpyDeviceToHost, st));
+  PKV_CUDA(cudaStreamSynchronize(st));
+  if (v) {
+    PKV_CUDA(cudaMemsetAsync(dev_word, 0, sizeof v, st));
+    PKV_CUDA(cudaStreamSynchronize(st));
+  }
+  if (out) *out = v;
+  return PKV_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* pkv_last_error(void) { return g_err.c_str(); }
+int pkv_abi_version(void) { return PKV_ABI_VERSION; }
+
+int pkv_shard_create(pkv_shard** out, int device, int max_batch, int n_q_heads) {
+  if (!out) return fail(PKV_E_INVALID, "null out");
+  if (max_batch <= 0 || max_batch > pkv::kMaxBatch)
+    return fail(PKV_E_INVALID, "max_batch %d outside [1, %d]", max_batch, pkv::kMaxBatch);
+  if (n_q_heads <= 0 || n_q_heads > 1024) return fail(PKV_E_INVALID, "n_q_heads %d", n_q_heads);
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", device);
+  int sms = 0, major = 0;
+  PKV_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  PKV_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+  if (major != 10)
+    return fail(PKV_E_UNSUPPORTED, "device %d has compute capability %d.x; this library is sm_100a only",
+                device, major);
+  pkv_shard* s = new pkv_shard();
+  s->device = device;
+  s->num_sms = sms;
+  s->max_batch = max_batch;
+  s->n_q_heads = n_q_heads;
+  s->n_slots = sms + max_batch;
+  s->maps.reserve(32);
+  const size_t o_bytes = (size_t)s->n_slots * n_q_heads * pkv::kHeadDim * sizeof(float);
+  const size_t ml_bytes = (size_t)s->n_slots * n_q_heads * 2 * sizeof(float);
+  cudaError_t e = cudaMalloc(&s->part_o, o_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&s->part_ml, ml_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&s->status, 256);
+  if (e == cudaSuccess) e = cudaMemset(s->status, 0, 256);
+  if (e != cudaSuccess) {
+    pkv_shard_destroy(s);
+    return fail(PKV_E_CUDA, "scratch allocation failed: %s", cudaGetErrorString(e));
+  }
+  s->done_counter = reinterpret_cast<unsigned int*>(s->status) + 16;
+  *out = s;
+  return PKV_OK;
+}
+
+int pkv_shard_destroy(pkv_shard* s) {
+  if (!s) return PKV_OK;
+  DeviceGuard guard(s->device);
+  cudaFree(s->part_o);
+  cudaFree(s->part_ml);
+  cudaFree(s->status);
+  delete s;
+  return PKV_OK;
+}
+
+int pkv_shard_status(pkv_shard* s, void* stream, uint32_t* status_out) {
+  if (!s) return fail(PKV_E_INVALID, "null shard");
+  return read_status(s->device, s->status, static_cast<cudaStream_t>(stream), status_out);
+}
+
+int pkv_decode_partial(pkv_shard* s, const pkv_decode_args* a, float* o_part, float* lse_part,
+                       void* stream) {
+  if (!o_part || !lse_part) return fail(PKV_E_INVALID, "null o_part or lse_part");
+  LaunchOut lo;
+  lo.o_part = o_part;
+  lo.lse_part = lse_part;
+  return launch_decode(s, a, lo, static_cast<cudaStream_t>(stream));
+}
+
+int pkv_decode(pkv_shard* s, const pkv_decode_args* a, void* out, int32_t out_dtype,
+               float* lse_out, void* stream) {
+  if (!out) return fail(PKV_E_INVALID, "null out");
+  if (out_dtype != PKV_F16 && out_dtype != PKV_BF16 && out_dtype != PKV_F32)
+    return fail(PKV_E_INVALID, "out_dtype %d", out_dtype);
+  LaunchOut lo;
+  lo.out = out;
+  lo.out_dtype = out_dtype;
+  lo.lse_part = lse_out;
+  return launch_decode(s, a, lo, static_cast<cudaStream_t>(stream));
+}
+
+int pkv_merge_partials(int device, const float* o_parts, int64_t o_part_stride,
+                       const float* lse_parts, int64_t lse_part_stride, int32_t n_parts,
+                       int32_t rows, int32_t head_dim, void* out, int32_t out_dtype,
+                       float* lse_out, void* stream) {
+  if (!o_parts || !lse_parts || !out) return fail(PKV_E_INVALID, "null pointer");
+  if (head_dim != pkv::kHeadDim) return fail(PKV_E_UNSUPPORTED, "head_dim %d: 128 required", head_dim);
+  if (n_parts <= 0 || rows < 0) return fail(PKV_E_INVALID, "n_parts %d rows %d", n_parts, rows);
+  if (out_dtype != PKV_F16 && out_dtype != PKV_BF16 && out_dtype != PKV_F32)
+    return fail(PKV_E_INVALID, "out_dtype %d", out_dtype);
+  if (rows == 0) return PKV_OK;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", device);
+  pkv::MergeParams m;
+  memset(&m, 0, sizeof m);
+  m.o_parts = o_parts; m.lse_parts = lse_parts;
+  m.o_stride = o_part_stride; m.lse_stride = lse_part_stride;
+  m.n_parts = n_parts; m.rows = rows;
+  m.out = out; m.out_dtype = out_dtype; m.lse_out = lse_out;
+  pkv::merge_partials_kernel<<<(rows + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(m);
+  PKV_CUDA(cudaGetLastError());
+  return PKV_OK;
+}
+
+int pkv_quantize_kv(int device, const void* src, int32_t src_dtype, int64_t rows, void* codes,
+                    void* scales, int32_t fmt, void* stream) {
+  if (!src || !codes || !scales) return fail(PKV_E_INVALID, "null pointer");
+  if (!is_16bit(src_dtype)) return fail(PKV_E_INVALID, "src_dtype must be PKV_F16 or PKV_BF16");
+  if (!is_quant(fmt)) return fail(PKV_E_INVALID, "fmt must be PKV_INT8 or PKV_FP8_E4M3");
+  if (rows < 0 || rows > (int64_t)0x7fffffff * 8) return fail(PKV_E_INVALID, "rows %lld", (long long)rows);
+  if (rows == 0) return PKV_OK;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", device);
+  const unsigned int blocks = static_cast<unsigned int>((rows + 7) / 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (src_dtype == PKV_BF16)
+    pkv::quantize_kv_kernel<true><<<blocks, 256, 0, st>>>(src, rows, static_cast<uint8_t*>(codes),
+                                                          static_cast<__half*>(scales), fmt);
+  else
+    pkv::quantize_kv_kernel<false><<<blocks, 256, 0, st>>>(src, rows, static_cast<uint8_t*>(codes),
+                                                           static_cast<__half*>(scales), fmt);
+  PKV_CUDA(cudaGetLastError());
+  return PKV_OK;
+}
+
+
+int pkv_split_block_table(int device, const int32_t* block_table, int64_t block_table_stride,
+                          const int32_t* seq_lens, int32_t batch, int32_t page_size,
+                          int32_t n_dev, int32_t mode, const int64_t* bases,
+                          int32_t* const* out_tables, int64_t out_stride,
+                          int32_t* const* out_lens, void* stream) {
+  if (!block_table || !seq_lens || !out_tables || !out_lens) return fail(PKV_E_INVALID, "null pointer");
+  if (n_dev < 1 || n_dev > pkv::kMaxWorld) return fail(PKV_E_INVALID, "n_dev %d", n_dev);
+  if (mode != 0 && mode != 1) return fail(PKV_E_INVALID, "mode %d", mode);
+  if (mode == 0 && !bases) return fail(PKV_E_INVALID, "mode 0 needs bases");
+  if (page_size <= 0 || batch < 0) return fail(PKV_E_INVALID, "page_size %d batch %d", page_size, batch);
+  if (batch == 0) return PKV_OK;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", device);
+  pkv::SplitParams p;
+  memset(&p, 0, sizeof p);
+  p.block_table = block_table; p.seq_lens = seq_lens; p.bt_stride = block_table_stride;
+  p.batch = batch; p.page_size = page_size; p.n_dev = n_dev; p.mode = mode;
+  p.out_stride = out_stride;
+  for (int d = 0; d < n_dev; ++d) {
+    p.bases[d] = bases ? bases[d] : 0;
+    if (!out_tables[d] || !out_lens[d]) return fail(PKV_E_INVALID, "null output for device %d", d);
+    p.out_table[d] = out_tables[d];
+    p.out_lens[d] = out_lens[d];
+  }
+  pkv::split_block_table_kernel<<<dim3(batch, n_dev), 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  PKV_CUDA(cudaGetLastError());
+  return PKV_OK;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------- //
+// several GPUs
+// ------------------------------------------------------------------------- //
+struct pkv_exchange {
+  int device = 0, rank = 0, world = 1, max_batch = 0, n_q_heads = 0;
+  uint8_t* slab = nullptr;                  // this GPU's mailboxes (cudaMalloc)
+  uint8_t* peer_slab[pkv::kMaxWorld] = {};  // mapped slabs by rank (own slab at [rank])
+  bool imported[pkv::kMaxWorld] = {};       // opened with cudaIpcOpenMemHandle
+  uint32_t* status = nullptr;               // local: status word + counters
+  uint64_t epoch = 0;
+  size_t off_q = 0, off_o = 0, off_lse = 0, off_flags = 0, slab_bytes = 0;
+  size_t o_part_elems = 0, lse_part_elems = 0;
+};
+
+namespace {
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+float* slot_o(pkv_exchange* x, int owner_rank, int slot) {
+  return reinterpret_cast<float*>(x->peer_slab[owner_rank] + x->off_o) + (size_t)slot * x->o_part_elems;
+}
+float* slot_lse(pkv_exchange* x, int owner_rank, int slot) {
+  return reinterpret_cast<float*>(x->peer_slab[owner_rank] + x->off_lse) + (size_t)slot * x->lse_part_elems;
+}
+uint64_t* flag_ptr(pkv_exchange* x, int owner_rank, int idx) {   // idx world = q flag
+  return reinterpret_cast<uint64_t*>(x->peer_slab[owner_rank] + x->off_flags) + idx;
+}
+
+}  // namespace
+
+extern "C" {
+
+int pkv_exchange_create(pkv_exchange** out, int device, int rank, int world, int max_batch,
+                        int n_q_heads) {
+  if (!out) return fail(PKV_E_INVALID, "null out");
+  if (world < 1 || world > pkv::kMaxWorld || rank < 0 || rank >= world)
+    return fail(PKV_E_INVALID, "rank %d / world %d (max %d)", rank, world, pkv::kMaxWorld);
+  if (max_batch <= 0 || max_batch > pkv::kMaxBatch || n_q_heads <= 0)
+    return fail(PKV_E_INVALID, "max_batch %d n_q_heads %d", max_batch, n_q_heads);
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", device);
+  pkv_exchange* x = new pkv_exchange();
+  x->device = device; x->rank = rank; x->world = world;
+  x->max_batch = max_batch; x->n_q_heads = n_q_heads;
+  x->o_part_elems = (size_t)max_batch * n_q_heads * pkv::kHeadDim;
+  x->lse_part_elems = align_up((size_t)max_batch * n_q_heads, 64);
+  x->off_q = 0;
+  x->off_o = align_up((size_t)max_batch * n_q_heads * pkv::kHeadDim * 2, 256);
+  x->off_lse = x->off_o + align_up(world * x->o_part_elems * sizeof(float), 256);
+  x->off_flags = x->off_lse + align_up(world * x->lse_part_elems * sizeof(float), 256);
+  x->slab_bytes = x->off_flags + align_up((world + 1) * sizeof(uint64_t), 256);
+  cudaError_t e = cudaMalloc(&x->slab, x->slab_bytes);
+  if (e == cudaSuccess) e = cudaMemset(x->slab, 0, x->slab_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&x->status, 512);
+  if (e == cudaSuccess) e = cudaMemset(x->status, 0, 512);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    pkv_exchange_destroy(x);
+    return fail(PKV_E_CUDA, "mailbox allocation failed: %s", cudaGetErrorString(e));
+  }
+  x->peer_slab[rank] = x->slab;
+  *out = x;
+  return PKV_OK;
+}
+
+int pkv_exchange_destroy(pkv_exchange* x) {
+  if (!x) return PKV_OK;
+  DeviceGuard guard(x->device);
+  cudaDeviceSynchronize();
+  for (int r = 0; r < x->world; ++r)
+    if (x->imported[r] && x->peer_slab[r]) cudaIpcCloseMemHandle(x->peer_slab[r]);
+  cudaFree(x->slab);
+  cudaFree(x->status);
+  delete x;
+  return PKV_OK;
+}
+
+int pkv_exchange_export(pkv_exchange* x, void* handle64) {
+  if (!x || !handle64) return fail(PKV_E_INVALID, "null pointer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  DeviceGuard guard(x->device);
+  cudaIpcMemHandle_t h;
+  PKV_CUDA(cudaIpcGetMemHandle(&h, x->slab));
+  memcpy(handle64, &h, 64);
+  return PKV_OK;
+}
+
+int pkv_exchange_import(pkv_exchange* x, int peer_rank, const void* handle64) {
+  if (!x || !handle64) return fail(PKV_E_INVALID, "null pointer");
+  if (peer_rank < 0 || peer_rank >= x->world || peer_rank == x->rank)
+    return fail(PKV_E_INVALID, "peer_rank %d", peer_rank);
+  DeviceGuard guard(x->device);
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  PKV_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  x->peer_slab[peer_rank] = static_cast<uint8_t*>(p);
+  x->imported[peer_rank] = true;
+  return PKV_OK;
+}
+
+int pkv_exchange_attach(pkv_exchange* x, int peer_rank, pkv_exchange* peer) {
+  if (!x || !peer) return fail(PKV_E_INVALID, "null pointer");
+  if (peer_rank < 0 || peer_rank >= x->world || peer_rank == x->rank || peer->rank != peer_rank)
+    return fail(PKV_E_INVALID, "peer_rank %d", peer_rank);
+  if (peer->world != x->world || peer->max_batch != x->max_batch || peer->n_q_heads != x->n_q_heads)
+    return fail(PKV_E_INVALID, "exchanges were created with different shapes");
+  if (peer->device != x->device) {
+    DeviceGuard guard(x->device);
+    int can = 0;
+    PKV_CUDA(cudaDeviceCanAccessPeer(&can, x->device, peer->device));
+    if (!can) return fail(PKV_E_UNSUPPORTED, "device %d cannot access device %d", x->device, peer->device);
+    cudaError_t e = cudaDeviceEnablePeerAccess(peer->device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+    else if (e != cudaSuccess)
+      return fail(PKV_E_CUDA, "cudaDeviceEnablePeerAccess(%d): %s", peer->device, cudaGetErrorString(e));
+  }
+  x->peer_slab[peer_rank] = peer->slab;
+  return PKV_OK;
+}
+
+int pkv_exchange_status(pkv_exchange* x, void* stream, uint32_t* status_out) {
+  if (!x) return fail(PKV_E_INVALID, "null exchange");
+  return read_status(x->device, x->status, static_cast<cudaStream_t>(stream), status_out);
+}
+
+int pkv_exchange_epoch(pkv_exchange* x, uint64_t* epoch_out) {
+  if (!x || !epoch_out) return fail(PKV_E_INVALID, "null pointer");
+  *epoch_out = x->epoch;
+  return PKV_OK;
+}
+
+int pkv_home_publish_q(pkv_exchange* x, const void* q, int32_t batch, void* stream) {
+  if (!x || !q) return fail(PKV_E_INVALID, "null pointer");
+  if (batch <= 0 || batch > x->max_batch) return fail(PKV_E_INVALID, "batch %d", batch);
+  if (reinterpret_cast<uintptr_t>(q) & 15) return fail(PKV_E_INVALID, "q must be 16-byte aligned");
+  x->epoch += 1;
+  pkv::PublishParams p;
+  memset(&p, 0, sizeof p);
+  p.q = static_cast<const uint4*>(q);
+  p.n16 = (int64_t)batch * x->n_q_heads * pkv::kHeadDim * 2 / 16;
+  p.epoch = x->epoch;
+  p.counter = reinterpret_cast<unsigned int*>(x->status) + 32;
+  int n = 0;
+  for (int r = 0; r < x->world; ++r) {
+    if (r == x->rank) continue;
+    if (!x->peer_slab[r]) return fail(PKV_E_STATE, "rank %d is not attached", r);
+    p.dst[n] = reinterpret_cast<uint4*>(x->peer_slab[r] + x->off_q);
+    p.flag[n] = flag_ptr(x, r, x->world);
+    ++n;
+  }
+  p.n_dst = n;
+  if (n == 0) return PKV_OK;
+  DeviceGuard guard(x->device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", x->device);
+  int bx = static_cast<int>((p.n16 + 255) / 256);
+  if (bx > 16) bx = 16;
+  pkv::publish_q_kernel<<<dim3(bx, n), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  PKV_CUDA(cudaGetLastError());
+  return PKV_OK;
+}
+
+int pkv_peer_step(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, int32_t home_rank,
+                  int32_t q_override, void* stream) {
+  if (!x || !s || !a) return fail(PKV_E_INVALID, "null pointer");
+  if (home_rank < 0 || home_rank >= x->world || home_rank == x->rank)
+    return fail(PKV_E_INVALID, "home_rank %d", home_rank);
+  if (!x->peer_slab[home_rank]) return fail(PKV_E_STATE, "home rank %d is not attached", home_rank);
+  if (a->batch <= 0 || a->batch > x->max_batch) return fail(PKV_E_INVALID, "batch %d", a->batch);
+  if (a->n_q_heads != x->n_q_heads) return fail(PKV_E_INVALID, "n_q_heads mismatch");
+  x->epoch += 1;
+  pkv_decode_args aa = *a;
+  LaunchOut lo;
+  if (!q_override) {
+    aa.q = x->slab + x->off_q;
+    lo.q_flag = flag_ptr(x, x->rank, x->world);
+    lo.q_epoch = x->epoch;
+  }
+  lo.o_part = slot_o(x, home_rank, x->rank);
+  lo.lse_part = slot_lse(x, home_rank, x->rank);
+  lo.done_flag = flag_ptr(x, home_rank, x->rank);
+  lo.done_epoch = x->epoch;
+  return launch_decode(s, &aa, lo, static_cast<cudaStream_t>(stream));
+}
+
+int pkv_home_partial(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, void* stream) {
+  if (!x || !s || !a) return fail(PKV_E_INVALID, "null pointer");
+  if (a->batch <= 0 || a->batch > x->max_batch) return fail(PKV_E_INVALID, "batch %d", a->batch);
+  if (a->n_q_heads != x->n_q_heads) return fail(PKV_E_INVALID, "n_q_heads mismatch");
+  LaunchOut lo;
+  lo.o_part = slot_o(x, x->rank, x->rank);
+  lo.lse_part = slot_lse(x, x->rank, x->rank);
+  return launch_decode(s, a, lo, static_cast<cudaStream_t>(stream));
+}
+
+int pkv_home_merge(pkv_exchange* x, int32_t batch, uint32_t wait_mask, void* out,
+                   int32_t out_dtype, float* lse_out, void* stream) {
+  if (!x || !out) return fail(PKV_E_INVALID, "null pointer");
+  if (batch <= 0 || batch > x->max_batch) return fail(PKV_E_INVALID, "batch %d", batch);
+  if (out_dtype != PKV_F16 && out_dtype != PKV_BF16 && out_dtype != PKV_F32)
+    return fail(PKV_E_INVALID, "out_dtype %d", out_dtype);
+  DeviceGuard guard(x->device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", x->device);
+  pkv::MergeParams m;
+  memset(&m, 0, sizeof m);
+  m.o_parts = slot_o(x, x->rank, 0);
+  m.lse_parts = slot_lse(x, x->rank, 0);
+  m.o_stride = (int64_t)x->o_part_elems;
+  m.lse_stride = (int64_t)x->lse_part_elems;
+  m.n_parts = x->world;
+  m.rows = batch * x->n_q_heads;
+  m.out = out; m.out_dtype = out_dtype; m.lse_out = lse_out;
+  m.flags = flag_ptr(x, x->rank, 0);
+  m.wait_mask = wait_mask & ~(1u << x->rank);
+  m.epoch = x->epoch;
+  m.timeout_ns = kWaitNs;
+  m.status = x->status;
+  pkv::merge_partials_kernel<<<(m.rows + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(m);
+  PKV_CUDA(cudaGetLastError());
+  return PKV_OK;
+}
+
+}  // extern "C"

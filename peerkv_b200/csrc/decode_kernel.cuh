@@ -1,0 +1,504 @@
+// Paged, GQA-packed split-K flash-decode partial kernel for one KV shard (sm_100a).
+//
+// Replaces attn_split_gqa (PeerKV csrc/peer_attn_kernels.cuh:14-47) and the
+// per-sequence gather of umallm/peerkv/paged.py:48-97: the kernel walks the block
+// table itself and never copies KV.
+//
+// Work unit = a TILE of 16 tokens of one page, all (up to 8) kv-heads.  The tiles
+// of all sequences form one flat list; the grid is persistent (one CTA per SM) and
+// CTA c owns the contiguous range [c*per, (c+1)*per) of it, so load is balanced by
+// tokens, not by sequences.  Where a range crosses a sequence boundary the CTA
+// flushes one partial (unnormalised O, running max m, running sum l) to slot
+// c + seq; a sequence is therefore covered by the consecutive slots of the CTAs
+// that touched it and decode_combine_kernel merges them.
+//
+// Inside a CTA: warp 8 is the producer, 32 lanes issuing one 2 KiB TMA box each
+// per stage (K and V: 8 heads x 2 halves of the head dimension, [16 tok][64 d],
+// 128-byte swizzle so ldmatrix is bank-conflict free); warps 0..7 each own one
+// kv-head and consume the stage with tensor-core MMAs in the "swapped" form
+//     S^T[16 tok x 8 qheads] = K[16 x 128] . Q^T[128 x 8]
+//     O^T[128 d  x 8 qheads] += V^T[128 x 16] . P^T[16 x 8]
+// so the G = Hq/Hkv query heads of a group ride in the N = 8 dimension and one
+// K/V read serves the whole group.  Softmax statistics are per column (q head),
+// reduced with three xor-shuffles; P is transposed into the B-fragment layout
+// with movmatrix.  Decode is HBM-bound: the tensor cores are used because the
+// CUDA-core form needs ~8 issue cycles per KV row, more than HBM leaves.
+#pragma once
+#include "ptx.cuh"
+
+namespace pkv {
+
+constexpr int kHeadDim = 128;
+constexpr int kTileTok = 16;
+constexpr int kHeadsPerCta = 8;
+constexpr int kConsumerWarps = 8;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kMaxBatch = 4096;
+
+constexpr uint32_t kPollLimit = 1u << 22;  // polls of mbarrier.try_wait before giving up
+
+enum : uint32_t {
+  kStPipeTimeout = 0x1u,
+  kStBadPage = 0x2u,
+  kStQTimeout = 0x4u,
+  kStPartialTimeout = 0x8u,
+};
+
+struct DecodeParams {
+  const void* q;               // [B][Hq][128] 16-bit
+  const int32_t* block_table;  // may be null (identity)
+  const int32_t* seq_lens;     // [B]
+  const void* k_scale;         // quantised pools only: fp16 [page][tok][head]
+  const void* v_scale;
+  int64_t bt_stride;
+  int64_t n_pages;
+  int batch;
+  int n_q_heads;
+  int n_kv_heads;
+  int group;           // n_q_heads / n_kv_heads, 1..8
+  int page_size;       // tokens per page
+  int tiles_per_page;  // ceil(page_size / 16)
+  int head_major;      // 1: pool dims are (d, tok, head, page); 0: (d, head, tok, page)
+  int n_cta_x;
+  float scale_log2;    // softmax scale * log2(e)
+  float* part_o;       // [slots][Hq][128]
+  float* part_ml;      // [slots][Hq][2]  (m in log2 units, l)
+  uint32_t* status;
+  const uint64_t* q_flag;  // null, or: wait until *q_flag >= q_epoch before reading q
+  uint64_t q_epoch;
+  uint64_t q_timeout_ns;
+};
+
+// Tiles of a sequence with `len` tokens in this shard.
+__device__ __forceinline__ int seq_tiles(int len, int page_size, int tiles_per_page) {
+  int full = len / page_size;
+  int rem = len - full * page_size;
+  return full * tiles_per_page + (rem + kTileTok - 1) / kTileTok;
+}
+
+// Exclusive prefix of tiles per sequence into smem `prefix[0..batch]`.
+// Called by all threads of the block; ends with a __syncthreads().
+__device__ __forceinline__ void build_tile_prefix(int* prefix, const int32_t* seq_lens, int batch,
+                                                  int page_size, int tiles_per_page) {
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  for (int b = tid; b < batch; b += nthr) {
+    int len = seq_lens[b];
+    prefix[b + 1] = len > 0 ? seq_tiles(len, page_size, tiles_per_page) : 0;
+  }
+  if (tid == 0) prefix[0] = 0;
+  __syncthreads();
+  if (tid < 32) {
+    int carry = 0;
+    for (int base = 1; base <= batch; base += 32) {
+      int i = base + tid;
+      int v = i <= batch ? prefix[i] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, v, o);
+        if (tid >= o) v += n;
+      }
+      v += carry;
+      if (i <= batch) prefix[i] = v;
+      carry = __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  __syncthreads();
+}
+
+// Largest s with prefix[s] <= g (prefix non-decreasing, prefix[batch] > g).
+__device__ __forceinline__ int find_seq(const int* prefix, int batch, int g) {
+  int lo = 0, hi = batch;
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (prefix[mid] <= g) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+template <int NSTAGE>
+struct SmemLayout {
+  static constexpr int kKBytes = kHeadsPerCta * kTileTok * kHeadDim * 2;  // 32 KiB
+  static constexpr int kStageBytes = 2 * kKBytes;
+  static constexpr int kDataBytes = NSTAGE * kStageBytes;
+  static constexpr int kBarOff = kDataBytes;                 // 3*NSTAGE barriers
+  static constexpr int kAbortOff = kBarOff + 3 * NSTAGE * 8;
+  static constexpr int kPrefixOff = kAbortOff + 16;
+  static constexpr int kTotal = kPrefixOff + (kMaxBatch + 1) * 4 + 1024;  // +1024: manual alignment
+};
+
+template <bool BF16, int NSTAGE>
+__global__ void __launch_bounds__(kThreads, 1)
+decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_v, const DecodeParams p) {
+  using L = SmemLayout<NSTAGE>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
+  int* prefix = reinterpret_cast<int*>(sgen + L::kPrefixOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kAbortOff);
+  const uint32_t bar0 = sbase + L::kBarOff;
+  auto kfull = [&](int s) { return bar0 + 8u * s; };
+  auto vfull = [&](int s) { return bar0 + 8u * (NSTAGE + s); };
+  auto empty = [&](int s) { return bar0 + 8u * (2 * NSTAGE + s); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hb = blockIdx.y;                   // block of 8 kv-heads
+  const int head0 = hb * kHeadsPerCta;
+  const int heads_here = min(kHeadsPerCta, p.n_kv_heads - head0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NSTAGE; ++s) {
+      mbar_init(kfull(s), 1);
+      mbar_init(vfull(s), 1);
+      mbar_init(empty(s), kConsumerWarps);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  build_tile_prefix(prefix, p.seq_lens, p.batch, p.page_size, p.tiles_per_page);
+
+  const int total = prefix[p.batch];
+  const int per = (total + p.n_cta_x - 1) / p.n_cta_x;
+  const int g0 = min(total, (int)blockIdx.x * per);
+  const int g1 = min(total, g0 + per);
+  if (g0 >= g1) return;
+
+  if (warp == kConsumerWarps) {
+    // ------------------------------ producer ------------------------------ //
+    if (lane == 0) { prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v); }
+    // lane -> (K or V, head, half of the head dimension)
+    const int is_v = lane >> 4;
+    const int hh = (lane >> 1) & 7;
+    const int dh = lane & 1;
+    const bool lane_active = hh < heads_here;
+    const uint32_t dst_off = (is_v ? L::kKBytes : 0) + hh * 4096 + dh * 2048;
+    const CUtensorMap* map = is_v ? &tm_v : &tm_k;
+    const uint32_t bytes_half = heads_here * 4096;
+
+    int s = find_seq(prefix, p.batch, g0);
+    int it = 0;
+    bool ok = true;
+    for (int g = g0; g < g1 && ok;) {
+      while (prefix[s + 1] <= g) ++s;
+      const int seg_end = min(g1, prefix[s + 1]);
+      int ti = g - prefix[s];                       // tile index inside the sequence
+      const int n = seg_end - g;
+      for (int base = 0; base < n && ok; base += 32) {
+        // one coalesced block-table read per 32 tiles
+        const int my_tile = ti + base + lane;
+        int my_page = 0;
+        if (base + lane < n) {
+          const int pj = my_tile / p.tiles_per_page;
+          my_page = p.block_table ? p.block_table[(int64_t)s * p.bt_stride + pj]
+                                  : (int)((int64_t)s * p.bt_stride + pj);
+          if (my_page < 0 || my_page >= p.n_pages) {
+            atomicOr(p.status, kStBadPage);
+            my_page = 0;
+          }
+        }
+        const int cnt = min(32, n - base);
+        for (int j = 0; j < cnt; ++j, ++it) {
+          const int stage = it % NSTAGE;
+          const uint32_t ph = (it / NSTAGE) & 1;
+          const int page = __shfl_sync(0xffffffffu, my_page, j);
+          const int tok0 = ((ti + base + j) % p.tiles_per_page) * kTileTok;
+          bool got = true;
+          if (lane == 0) {
+            got = false;
+            for (uint32_t w = 0; w < kPollLimit; ++w) {
+              if (mbar_try_wait(empty(stage), ph ^ 1)) { got = true; break; }
+              if (*abort_flag) break;
+            }
+            if (got) {
+              mbar_arrive_expect_tx(kfull(stage), bytes_half);
+              mbar_arrive_expect_tx(vfull(stage), bytes_half);
+            } else {
+              atomicOr(p.status, kStPipeTimeout);
+              *abort_flag = 1;
+            }
+          }
+          got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
+          if (!got) { ok = false; break; }
+          if (lane_active) {
+            const uint32_t dst = sbase + stage * L::kStageBytes + dst_off;
+            const uint32_t bar = is_v ? vfull(stage) : kfull(stage);
+            if (p.head_major) tma_load_4d(dst, map, bar, dh * 64, tok0, head0 + hh, page);
+            else              tma_load_4d(dst, map, bar, dh * 64, head0 + hh, tok0, page);
+          }
+        }
+      }
+      g = seg_end;
+    }
+    if (!ok) {
+      // Give copies already in flight a bounded chance to land before the CTA
+      // (and its shared memory) goes away.
+      if (lane == 0) {
+        for (int back = 1; back <= NSTAGE && back <= it; ++back) {
+          const int jt = it - back;
+          const int stage = jt % NSTAGE;
+          const uint32_t ph = (jt / NSTAGE) & 1;
+          mbar_wait_bounded(kfull(stage), ph, kPollLimit);
+          mbar_wait_bounded(vfull(stage), ph, kPollLimit);
+        }
+      }
+    }
+    return;
+  }
+
+  // -------------------------------- consumers -------------------------------- //
+  const int hh = warp;                          // kv-head inside the block of 8
+  const bool active = hh < heads_here;
+  const int kvh = head0 + hh;
+  const int g = lane >> 2, t = lane & 3;        // MMA fragment row / column-pair ids
+  const int G = p.group;
+  const uint32_t koff = hh * 4096;
+  const uint32_t voff = L::kKBytes + hh * 4096;
+  // ldmatrix lane addressing (row inside the [16 tok][64 d] swizzled block)
+  const int krow = lane & 15, kcsel = lane >> 4;
+  const int vrow = (lane & 7) + ((lane >> 4) << 3), vcsel = (lane >> 3) & 1;
+  const uint32_t krow_off = krow * 128, kx = krow & 7;
+  const uint32_t vrow_off = vrow * 128, vx = vrow & 7;
+
+  bool q_ready = (p.q_flag == nullptr);
+
+  int s = find_seq(prefix, p.batch, g0);
+  int it = 0;
+  for (int gt = g0; gt < g1;) {
+    while (prefix[s + 1] <= gt) ++s;
+    const int seg_end = min(g1, prefix[s + 1]);
+    const int len = p.seq_lens[s];
+
+    if (!q_ready) {
+      // The query of this epoch is pushed by the home GPU; wait for its flag.
+      int okq = 1;
+      if (lane == 0) {
+        uint64_t t0, now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        okq = 0;
+        for (;;) {
+          if (ld_acquire_sys_u64(p.q_flag) >= p.q_epoch) { okq = 1; break; }
+          if (*abort_flag) break;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+          if (now - t0 > p.q_timeout_ns) break;
+          __nanosleep(64);
+        }
+        if (!okq) { atomicOr(p.status, kStQTimeout); *abort_flag = 1; }
+      }
+      okq = __shfl_sync(0xffffffffu, okq, 0);
+      if (!okq) return;
+      q_ready = true;
+    }
+
+    // Q^T B-fragments: column n = g is q head kvh*G + g (zero beyond the group).
+    uint32_t qf[8][2];
+    {
+      const uint32_t* qrow = reinterpret_cast<const uint32_t*>(
+          reinterpret_cast<const uint16_t*>(p.q) +
+          ((int64_t)s * p.n_q_heads + (int64_t)kvh * G + g) * kHeadDim);
+      const bool have = active && g < G;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        qf[ks][0] = have ? __ldcg(qrow + ks * 8 + t) : 0u;
+        qf[ks][1] = have ? __ldcg(qrow + ks * 8 + 4 + t) : 0u;
+      }
+    }
+    float o[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    for (int ti = gt - prefix[s]; gt < seg_end; ++gt, ++ti, ++it) {
+      const int stage = it % NSTAGE;
+      const uint32_t ph = (it / NSTAGE) & 1;
+      // valid tokens of this tile
+      const int pj = ti / p.tiles_per_page;
+      const int tok0 = (ti - pj * p.tiles_per_page) * kTileTok;
+      const int valid = min(kTileTok, min(p.page_size - tok0, len - pj * p.page_size - tok0));
+      const uint32_t sk = sbase + stage * L::kStageBytes + koff;
+      const uint32_t sv = sbase + stage * L::kStageBytes + voff;
+
+      bool got = false;
+      for (uint32_t w = 0; w < kPollLimit; ++w) {
+        if (mbar_try_wait(kfull(stage), ph)) { got = true; break; }
+        if (*abort_flag) break;
+      }
+      if (!got) { if (lane == 0) { atomicOr(p.status, kStPipeTimeout); *abort_flag = 1; } return; }
+
+      float sc[4];
+      if (active) {
+        float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          uint32_t a[4];
+          const uint32_t chunk = ((ks & 3) << 1) | kcsel;
+          ldmatrix_x4(a, sk + (ks >> 2) * 2048 + krow_off + ((chunk ^ kx) << 4));
+          if (ks & 1) mma_16816<BF16>(sb, a, qf[ks][0], qf[ks][1]);
+          else        mma_16816<BF16>(sa, a, qf[ks][0], qf[ks][1]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sc[i] = (sa[i] + sb[i]) * p.scale_log2;
+        if (valid < kTileTok) {
+          if (g >= valid) { sc[0] = -INFINITY; sc[1] = -INFINITY; }
+          if (g + 8 >= valid) { sc[2] = -INFINITY; sc[3] = -INFINITY; }
+        }
+        // column (q head) maxima over the 16 tokens
+        float mx0 = fmaxf(sc[0], sc[2]), mx1 = fmaxf(sc[1], sc[3]);
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+          mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+        }
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float al0 = fast_exp2(m0 - mn0), al1 = fast_exp2(m1 - mn1);
+        m0 = mn0; m1 = mn1;
+        sc[0] = fast_exp2(sc[0] - mn0); sc[2] = fast_exp2(sc[2] - mn0);
+        sc[1] = fast_exp2(sc[1] - mn1); sc[3] = fast_exp2(sc[3] - mn1);
+        l0 = l0 * al0 + sc[0] + sc[2];
+        l1 = l1 * al1 + sc[1] + sc[3];
+        if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1;
+          }
+        }
+      }
+
+      got = false;
+      for (uint32_t w = 0; w < kPollLimit; ++w) {
+        if (mbar_try_wait(vfull(stage), ph)) { got = true; break; }
+        if (*abort_flag) break;
+      }
+      if (!got) { if (lane == 0) { atomicOr(p.status, kStPipeTimeout); *abort_flag = 1; } return; }
+
+      if (active) {
+        // P^T as the B operand: transpose the two 8x8 (tok x head) blocks.
+        const uint32_t b0 = movmatrix_trans(pack2<BF16>(sc[0], sc[1]));
+        const uint32_t b1 = movmatrix_trans(pack2<BF16>(sc[2], sc[3]));
+        // Rows of a partial tile beyond `valid` may hold anything (even NaN bit
+        // patterns): blank them in the A fragments instead of touching smem.
+        uint32_t mk01 = 0xffffffffu, mk23 = 0xffffffffu;
+        if (valid < kTileTok) {
+          mk01 = (2 * t < valid ? 0x0000ffffu : 0u) | (2 * t + 1 < valid ? 0xffff0000u : 0u);
+          mk23 = (2 * t + 8 < valid ? 0x0000ffffu : 0u) | (2 * t + 9 < valid ? 0xffff0000u : 0u);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint32_t a[4];
+          const uint32_t chunk = ((j & 3) << 1) | vcsel;
+          ldmatrix_x4_trans(a, sv + (j >> 2) * 2048 + vrow_off + ((chunk ^ vx) << 4));
+          a[0] &= mk01; a[1] &= mk01; a[2] &= mk23; a[3] &= mk23;
+          mma_16816<BF16>(o[j], a, b0, b1);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty(stage));
+    }
+
+    // flush this (CTA, sequence) partial
+    if (active) {
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+      }
+      const int slot = blockIdx.x + s;
+      const int64_t hbase = (int64_t)slot * p.n_q_heads + (int64_t)kvh * G;
+      const int h0 = 2 * t, h1 = 2 * t + 1;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int d = 16 * j + g;
+        if (h0 < G) {
+          p.part_o[(hbase + h0) * kHeadDim + d] = o[j][0];
+          p.part_o[(hbase + h0) * kHeadDim + d + 8] = o[j][2];
+        }
+        if (h1 < G) {
+          p.part_o[(hbase + h1) * kHeadDim + d] = o[j][1];
+          p.part_o[(hbase + h1) * kHeadDim + d + 8] = o[j][3];
+        }
+      }
+      if (g == 0) {
+        if (h0 < G) { p.part_ml[(hbase + h0) * 2] = m0; p.part_ml[(hbase + h0) * 2 + 1] = l0; }
+        if (h1 < G) { p.part_ml[(hbase + h1) * 2] = m1; p.part_ml[(hbase + h1) * 2 + 1] = l1; }
+      }
+    }
+  }
+}
+
+// Merge the per-CTA partials of each (sequence, q head) and either write the final
+// output or this shard's (O, lse) partial -- into local memory or, through a P2P
+// mapping, straight into the home GPU's slot.  Replaces attn_combine
+// (PeerKV csrc/peer_attn_kernels.cuh:50-61).
+struct CombineParams {
+  const int32_t* seq_lens;
+  const float* part_o;
+  const float* part_ml;
+  int batch, n_q_heads, page_size, tiles_per_page, n_cta_x;
+  void* out;        // [B][Hq][128] in out_dtype, or null
+  int out_dtype;    // 0 f16, 1 bf16, 4 f32
+  float* o_part;    // [B][Hq][128] f32 normalised, or null
+  float* lse_part;  // [B][Hq] natural log, or null
+  // completion signal (multi-GPU): the last block to finish releases *done_flag = done_epoch
+  unsigned int* done_counter;  // local, zero between launches
+  uint64_t* done_flag;         // may live on another GPU
+  uint64_t done_epoch;
+};
+
+__device__ __forceinline__ void store_out(void* out, int dtype, int64_t idx, float v) {
+  if (dtype == 4) reinterpret_cast<float*>(out)[idx] = v;
+  else if (dtype == 1) reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
+  else reinterpret_cast<__half*>(out)[idx] = __float2half_rn(v);
+}
+
+constexpr int kCombineHeads = 4;  // q heads per combine block (one warp-quad of 128 threads each)
+
+__global__ void __launch_bounds__(128 * kCombineHeads)
+decode_combine_kernel(const CombineParams p) {
+  extern __shared__ int prefix_sm[];
+  build_tile_prefix(prefix_sm, p.seq_lens, p.batch, p.page_size, p.tiles_per_page);
+  const int b = blockIdx.x;
+  const int h = blockIdx.y * kCombineHeads + (threadIdx.x >> 7);
+  const int d = threadIdx.x & 127;
+  if (h < p.n_q_heads) {
+    const int total = prefix_sm[p.batch];
+    const int per = (total + p.n_cta_x - 1) / max(p.n_cta_x, 1);
+    const int t0 = prefix_sm[b], t1 = prefix_sm[b + 1];
+    float m = -INFINITY, l = 0.f, acc = 0.f;
+    if (t1 > t0) {
+      const int c0 = t0 / per, c1 = (t1 - 1) / per;
+      for (int c = c0; c <= c1; ++c) {
+        const int64_t row = (int64_t)(c + b) * p.n_q_heads + h;
+        const float ms = p.part_ml[row * 2], ls = p.part_ml[row * 2 + 1];
+        const float os = p.part_o[row * kHeadDim + d];
+        const float mn = fmaxf(m, ms);
+        const float ca = exp2f(m - mn), cs = exp2f(ms - mn);
+        l = l * ca + ls * cs;
+        acc = acc * ca + os * cs;
+        m = mn;
+      }
+    }
+    const float o = l > 0.f ? acc / l : 0.f;
+    const int64_t idx = ((int64_t)b * p.n_q_heads + h) * kHeadDim + d;
+    if (p.out) store_out(p.out, p.out_dtype, idx, o);
+    if (p.o_part) p.o_part[idx] = o;
+    if (p.lse_part && d == 0)
+      p.lse_part[(int64_t)b * p.n_q_heads + h] =
+          l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+  }
+  if (p.done_flag) {
+    // Every block publishes its stores system-wide, then counts in; the last one
+    // releases the flag that the home GPU's merge kernel waits on.
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int nblk = gridDim.x * gridDim.y;
+      const unsigned int prev = atomicAdd(p.done_counter, 1u);
+      if (prev == nblk - 1) {
+        *p.done_counter = 0;
+        __threadfence_system();
+        st_release_sys_u64(p.done_flag, p.done_epoch);
+      }
+    }
+  }
+}
+
+}  // namespace pkv

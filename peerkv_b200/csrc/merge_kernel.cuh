@@ -1,0 +1,222 @@
+// Cross-GPU exchange kernels: q publish (home -> peers, P2P stores), the single-pass
+// N-way LSE merge (with a bounded wait on the peers' epoch flags) and the KV
+// quantiser.  Replaces merge2_h (PeerKV csrc/peer_attn_kernels.cuh:64-73) and the
+// cudaMemcpyAsync + event fork/join of csrc/peer_fused_attn_ext.cu:100-102,112-128.
+#pragma once
+#include "decode_kernel.cuh"
+
+namespace pkv {
+
+constexpr int kMaxWorld = 16;
+
+struct PublishParams {
+  const uint4* q;          // [n16] 16-byte words of q
+  int64_t n16;
+  int n_dst;
+  uint4* dst[kMaxWorld];   // peers' q inboxes (P2P mapped)
+  uint64_t* flag[kMaxWorld];
+  uint64_t epoch;
+  unsigned int* counter;   // local, zero between launches
+};
+
+// grid.y = destination peer, grid.x blocks stride over q.  The last block of each
+// destination releases that peer's q flag.
+__global__ void __launch_bounds__(256) publish_q_kernel(const PublishParams p) {
+  const int dsti = blockIdx.y;
+  uint4* dst = p.dst[dsti];
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.n16;
+       i += (int64_t)gridDim.x * blockDim.x)
+    dst[i] = p.q[i];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(p.counter + dsti, 1u);
+    if (prev == gridDim.x - 1) {
+      p.counter[dsti] = 0;
+      __threadfence_system();
+      st_release_sys_u64(p.flag[dsti], p.epoch);
+    }
+  }
+}
+
+struct MergeParams {
+  const float* o_parts;     // part i at o_parts + i*o_stride: [rows][128]
+  const float* lse_parts;   // part i at lse_parts + i*lse_stride: [rows]
+  int64_t o_stride, lse_stride;
+  int n_parts, rows;
+  void* out;
+  int out_dtype;
+  float* lse_out;
+  // optional bounded wait: flags[i] >= epoch for every i with bit i of wait_mask
+  const uint64_t* flags;
+  uint32_t wait_mask;
+  uint64_t epoch;
+  uint64_t timeout_ns;
+  uint32_t* status;
+};
+
+// One warp per (sequence, q head) row; each lane owns 4 of the 128 output dims.
+__global__ void __launch_bounds__(256) merge_partials_kernel(const MergeParams p) {
+  __shared__ int s_ok;
+  if (p.flags && p.wait_mask) {
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < p.n_parts && ((p.wait_mask >> threadIdx.x) & 1u)) {
+      uint64_t t0, now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+      for (;;) {
+        if (ld_acquire_sys_u64(p.flags + threadIdx.x) >= p.epoch) break;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (now - t0 > p.timeout_ns) {
+          atomicOr(p.status, kStPartialTimeout);
+          s_ok = 0;
+          break;
+        }
+        __nanosleep(32);
+      }
+    }
+    __syncthreads();
+    if (!s_ok) return;   // status says why; the output is left untouched
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= p.rows) return;
+  float L = -INFINITY;
+  for (int i = 0; i < p.n_parts; ++i) L = fmaxf(L, __ldcg(p.lse_parts + i * p.lse_stride + row));
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float wsum = 0.f;
+  if (L > -INFINITY) {
+    for (int i = 0; i < p.n_parts; ++i) {
+      const float li = __ldcg(p.lse_parts + i * p.lse_stride + row);
+      if (li == -INFINITY) continue;
+      const float w = __expf(li - L);
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(
+                                  p.o_parts + i * p.o_stride + (int64_t)row * kHeadDim) + lane);
+      acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+      wsum += w;
+    }
+    const float inv = 1.f / wsum;
+    acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+  }
+  const int64_t idx = (int64_t)row * kHeadDim + lane * 4;
+  if (p.out_dtype == 4) {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + idx) = acc;
+  } else if (p.out_dtype == 1) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y), b = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 v = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + idx) = v;
+  } else {
+    __half2 a = __floats2half2_rn(acc.x, acc.y), b = __floats2half2_rn(acc.z, acc.w);
+    uint2 v = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+    *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + idx) = v;
+  }
+  if (p.lse_out && lane == 0) p.lse_out[row] = L > -INFINITY ? L + __logf(wsum) : -INFINITY;
+}
+
+// Per-row absmax quantiser (one warp per row of 128 values, 4 per lane).
+//   a = max|x|; s32 = a/QMAX (1 if a == 0); stored scale s = fp16_rn(s32), bumped to
+//   the smallest fp16 subnormal if that rounded to 0; code = q(x / float(s)) with a
+//   true fp32 division; int8: rint + clamp to +-127; e4m3: clamp to +-448 then RNE.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+quantize_kv_kernel(const void* __restrict__ src, int64_t rows, uint8_t* __restrict__ codes,
+                   __half* __restrict__ scales, int fmt) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= rows) return;
+  float x[4];
+  const uint2 raw = *(reinterpret_cast<const uint2*>(
+                          reinterpret_cast<const uint16_t*>(src) + row * kHeadDim) + lane);
+  if constexpr (BF16) {
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    x[0] = __low2float(a); x[1] = __high2float(a); x[2] = __low2float(b); x[3] = __high2float(b);
+  } else {
+    const __half2 a = *reinterpret_cast<const __half2*>(&raw.x);
+    const __half2 b = *reinterpret_cast<const __half2*>(&raw.y);
+    x[0] = __low2float(a); x[1] = __high2float(a); x[2] = __low2float(b); x[3] = __high2float(b);
+  }
+  float a = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, off));
+  const float qmax = fmt == 2 ? 127.f : 448.f;
+  float s32 = __fdiv_rn(a, qmax);
+  if (a == 0.f) s32 = 1.f;
+  __half s16 = __float2half_rn(s32);
+  if (__half2float(s16) == 0.f) s16 = __ushort_as_half((unsigned short)1);
+  const float sf = __half2float(s16);
+  uint32_t packed = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float y = __fdiv_rn(x[i], sf);
+    uint32_t c;
+    if (fmt == 2) {
+      const float r = fminf(fmaxf(rintf(y), -127.f), 127.f);
+      c = static_cast<uint32_t>(static_cast<int>(r)) & 0xffu;
+    } else {
+      const float yc = fminf(fmaxf(y, -448.f), 448.f);
+      uint16_t pr;
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pr) : "f"(0.f), "f"(yc));
+      c = pr & 0xffu;
+    }
+    packed |= c << (8 * i);
+  }
+  *(reinterpret_cast<uint32_t*>(codes + row * kHeadDim) + lane) = packed;
+  if (lane == 0) scales[row] = s16;
+}
+
+// Splits a global block table into per-GPU local tables (the device-side form of
+// the id test in PeerKV umallm/peerkv/paged.py:52-61, generalised to N GPUs).
+//   mode 0 (ranges):      owner d = largest d with bases[d] <= gid, local id = gid - bases[d]
+//   mode 1 (round robin): owner d = gid mod n_dev,                  local id = gid div n_dev
+// One warp per (sequence, device): a stable ballot compaction keeps sequence
+// order, so a sequence's partial last page stays last in its owner's list.
+struct SplitParams {
+  const int32_t* block_table;   // [batch][bt_stride] global ids
+  const int32_t* seq_lens;      // [batch] tokens
+  int64_t bt_stride;
+  int batch, page_size, n_dev, mode;
+  int64_t bases[kMaxWorld];
+  int32_t* out_table[kMaxWorld];  // [batch][out_stride] each; may be P2P mapped
+  int32_t* out_lens[kMaxWorld];   // [batch] each
+  int64_t out_stride;
+};
+
+__global__ void __launch_bounds__(32) split_block_table_kernel(const SplitParams p) {
+  const int b = blockIdx.x, d = blockIdx.y, lane = threadIdx.x;
+  const int len = p.seq_lens[b];
+  const int n_blk = len > 0 ? (len + p.page_size - 1) / p.page_size : 0;
+  const int32_t* row = p.block_table + (int64_t)b * p.bt_stride;
+  int32_t* out = p.out_table[d] + (int64_t)b * p.out_stride;
+  int cnt = 0;
+  bool owns_last = false;
+  for (int j0 = 0; j0 < n_blk; j0 += 32) {
+    const int j = j0 + lane;
+    bool mine = false;
+    int local = 0;
+    if (j < n_blk) {
+      const int64_t gid = row[j];
+      if (p.mode == 1) {
+        mine = (gid % p.n_dev) == d;
+        local = (int)(gid / p.n_dev);
+      } else {
+        int owner = 0;
+        for (int k = 1; k < p.n_dev; ++k) if (gid >= p.bases[k]) owner = k;
+        mine = owner == d;
+        local = (int)(gid - p.bases[d]);
+      }
+      if (mine && j == n_blk - 1) owns_last = true;
+    }
+    const unsigned int bal = __ballot_sync(0xffffffffu, mine);
+    if (mine) out[cnt + __popc(bal & ((1u << lane) - 1u))] = local;
+    cnt += __popc(bal);
+  }
+  owns_last = __any_sync(0xffffffffu, owns_last);
+  if (lane == 0) {
+    int tok = cnt * p.page_size;
+    if (owns_last) tok -= n_blk * p.page_size - len;
+    p.out_lens[d][b] = tok;
+  }
+}
+
+}  // namespace pkv

@@ -1,0 +1,70 @@
+"""One process per GPU (torchrun): the same step as group.PeerGroup, with the
+mailboxes shared across processes through CUDA IPC handles that travel over
+torch.distributed once, at set-up.  After that no collective runs on the data
+path: q is pushed and partials are gathered with P2P stores and epoch flags by
+the library's own kernels.
+
+Every rank calls `step(...)` once per decode step, in lockstep: rank `home`
+publishes q, computes its own partial and merges; the others compute theirs and
+push it.  Epochs count steps, so a rank that skips a step desynchronises the
+group (the waits are bounded: a missing q or partial ends as a status bit, not a
+hang).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _lib, ops
+from ._lib import PeerKVError, check
+from .group import Exchange
+
+
+class DistPeerGroup:
+    def __init__(self, device, max_batch: int, n_q_heads: int, home: int = 0, group=None):
+        if not dist.is_initialized():
+            raise PeerKVError("torch.distributed must be initialised first")
+        self.device = torch.device(device)
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.home = home
+        self.pg = group
+        self.shard = ops.Shard(self.device, max_batch, n_q_heads)
+        self.xchg = Exchange(self.device, self.rank, self.world, max_batch, n_q_heads)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.xchg.export_handle(), group=group)
+        for r, h in enumerate(handles):
+            if r != self.rank:
+                self.xchg.import_handle(r, h)
+        dist.barrier(group=group)
+
+    @property
+    def is_home(self) -> bool:
+        return self.rank == self.home
+
+    def step(self, args: _lib.DecodeArgs, q: Optional[torch.Tensor] = None,
+             out: Optional[torch.Tensor] = None):
+        """args describes THIS rank's shard (q inside it is used on the home rank only)."""
+        L = _lib.lib()
+        st = ops._stream(self.device)
+        if self.is_home:
+            B = args.batch
+            check(L.pkv_home_publish_q(self.xchg._h, q.data_ptr(), B, st))
+            check(L.pkv_home_partial(self.xchg._h, self.shard._h, C.byref(args), st))
+            mask = ((1 << self.world) - 1) & ~(1 << self.rank)
+            check(L.pkv_home_merge(self.xchg._h, B, mask, out.data_ptr(), ops._DT[out.dtype], None, st))
+            return out
+        check(L.pkv_peer_step(self.xchg._h, self.shard._h, C.byref(args), self.home, 0, st))
+        return None
+
+    def status(self) -> int:
+        return self.shard.status() | self.xchg.status()
+
+    def close(self):
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.pg)
+        self.xchg.close()
+        self.shard.close()
