@@ -1,0 +1,388 @@
+"""Benchmark of peer-parallel split-K decode attention on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (BASELINE configuration "batched paged decode attention"): batch 16,
+32 query / 8 kv heads, head_dim 128, 131072-token context per sequence, bf16 KV in
+16-token pages, block table = seeded random permutation of the page pool; for
+N > 1 page p lives on GPU p mod N (strong scaling: the same 8 GiB of KV is split),
+q is resident on GPU 0 and the partials are merged on GPU 0.  A step is one
+decode-attention layer.  Synthetic N(0,1) data.
+
+Prints ONE JSON line: effective KV GB/s (algorithmic KV bytes / step time) with
+the per-layer latency, the roofline of the dominant kernel, an end-to-end number
+with host buffers, and the CPU baseline (the oracle port of the reference's torch
+path, timed on this box's host cores).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+B, HQ, HKV, D, PAGE = 16, 32, 8, 128, 16
+CTX = 131072
+BYTES_PER_TOKEN = 2 * HKV * D * 2            # K and V, bf16
+PEAK_FALLBACK_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of decode_partial_kernel per launch,
+# measured with ncu on a 1 GiB pool and scaled by tokens (profiles/decode_partial_c2.md)
+NCU_TRAFFIC_PER_ALGO_BYTE = None
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return PEAK_FALLBACK_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read only)."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            import torch
+            uuid = str(torch.cuda.get_device_properties(index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            self.nv = pynvml
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # pragma: no cover
+            self.nv = None
+            self.err = repr(e)
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonGpuIdle", 0x1): "gpu_idle",
+            getattr(nv, "nvmlClocksEventReasonApplicationsClocksSetting", 0x2): "applications_clocks_setting",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSyncBoost", 0x10): "sync_boost",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80): "hw_power_brake_slowdown",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, n in names.items():
+                    if r & bit and n != "gpu_idle":
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def start(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._run, daemon=True)
+            self._thr.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join()
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# --------------------------------------------------------------------------- #
+# reference arm / cpu baseline: the oracle port on host cores
+# --------------------------------------------------------------------------- #
+def cpu_sample_inputs(tokens: int, seed: int = 0):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    n_pages = tokens // PAGE
+    pool = torch.randn(2, n_pages, PAGE, HKV, D, generator=g).bfloat16()
+    bt = torch.randperm(n_pages, generator=g).to(torch.int32).view(1, -1)
+    q = torch.randn(1, HQ, D, generator=g).bfloat16()
+    return q, pool, bt, torch.tensor([tokens], dtype=torch.int32)
+
+
+def cpu_reference_step(inputs, n_shards: int):
+    """The reference's path on CPU: per-sequence paged gather (peerkv/paged.py), one
+    partial per shard with GQA expansion and fp32 math, then the merge fold."""
+    from oracle import peerkv_oracle as orc
+    q, pool, bt, sl = inputs
+    tokens = int(sl[0])
+    n_pages = tokens // PAGE
+    per = n_pages // n_shards
+    shards = []
+    for s in range(n_shards):
+        ids = bt[0, s * per:(s + 1) * per].tolist() if s < n_shards - 1 else bt[0, s * per:].tolist()
+        K, V = orc.cat_blocks(pool, ids, len(ids) * PAGE)
+        shards.append((K.unsqueeze(0), V.unsqueeze(0)))
+    return orc.peer_parallel_attention(q.view(1, HQ, 1, D), shards)
+
+
+def run_reference(args):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    tokens = 32768
+    inputs = cpu_sample_inputs(tokens)
+    n_shards = max(1, args.gpus)
+    for _ in range(args.warmup):
+        cpu_reference_step(inputs, n_shards)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_reference_step(inputs, n_shards)
+    dt = (time.perf_counter() - t0) / args.steps
+    gbs = tokens * BYTES_PER_TOKEN / dt / 1e9
+    sample = f"1 sequence x {tokens} tokens of the workload per step, {n_shards} shard(s), paged gather + fp32 math + merge"
+    line = {
+        "impl": "reference", "metric": "decode_attn_effective_kv_bandwidth", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n):
+    return {"workload": "batched paged decode attention: batch 16, Hq 32, Hkv 8, head_dim 128, "
+                        "context 131072/seq, bf16, 16-token pages, random-permutation block table",
+            "batch": B, "context": CTX, "page_size": PAGE, "kv_bytes_per_layer": B * CTX * BYTES_PER_TOKEN,
+            "sharding": f"round-robin pages over {n} GPU(s), q and merge on GPU 0",
+            "l2_policy": "inputs larger than L2 (KV per GPU >= 1 GiB, read once per step)"}
+
+
+# --------------------------------------------------------------------------- #
+# our arm
+# --------------------------------------------------------------------------- #
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--context", type=int, default=CTX, help="tokens per sequence (parity/ncu runs use less)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--lean", action="store_true", help="timed steps only (for runs under a profiler)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from peerkv_b200 import _lib, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    N = args.gpus
+    if world != N:
+        raise SystemExit(f"--gpus {N} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {N}")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if N > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=dev)
+    ctx = args.context
+    assert ctx % PAGE == 0
+    pages_per_seq = ctx // PAGE
+    total_pages = B * pages_per_seq
+    assert total_pages % N == 0
+    n_local = total_pages // N
+
+    # global block table: the same seeded permutation on every rank
+    g = torch.Generator().manual_seed(1234)
+    bt_global = torch.randperm(total_pages, generator=g).to(torch.int32).view(B, pages_per_seq)
+    sl_global = torch.full((B,), ctx, dtype=torch.int32)
+    # this rank's pool (pages p with p mod N == rank), N(0,1) bf16
+    torch.manual_seed(100 + rank)
+    pool = torch.empty(2, n_local, PAGE, HKV, D, dtype=torch.bfloat16, device=dev)
+    chunk = max(1, n_local // 8)
+    for i in range(0, n_local, chunk):
+        pool[:, i:i + chunk].normal_()
+    # placement on the device: split the global table into this rank's local table
+    btd, sld = bt_global.to(dev), sl_global.to(dev)
+    tabs = [torch.zeros(B, pages_per_seq, dtype=torch.int32, device=dev) for _ in range(N)]
+    lens = [torch.zeros(B, dtype=torch.int32, device=dev) for _ in range(N)]
+    _lib.check(_lib.lib().pkv_split_block_table(
+        dev.index, btd.data_ptr(), pages_per_seq, sld.data_ptr(), B, PAGE, N, 1, None,
+        (C.c_void_p * N)(*[t.data_ptr() for t in tabs]), pages_per_seq,
+        (C.c_void_p * N)(*[t.data_ptr() for t in lens]), ops._stream(dev)))
+    torch.cuda.synchronize()
+    my_tab, my_len = tabs[rank], lens[rank]
+    local_tokens = int(my_len.sum())
+
+    torch.manual_seed(7)
+    q_host = torch.randn(B, HQ, D).bfloat16().pin_memory()
+    q = q_host.to(dev)
+    out = torch.empty(B, HQ, D, dtype=torch.bfloat16, device=dev)
+    out_host = torch.empty(B, HQ, D, dtype=torch.bfloat16).pin_memory()
+    tab_host = my_tab.cpu().pin_memory()
+    len_host = my_len.cpu().pin_memory()
+    scale = 1.0 / math.sqrt(D)
+    view = ops.paged_view(pool[0], pool[1])
+    L = _lib.lib()
+    st = ops._stream(dev)
+
+    if N == 1:
+        shard = ops.Shard(dev, B, HQ)
+        a = ops.make_args(q, view, my_tab, my_tab.stride(0), my_len, scale)
+
+        def step():
+            _lib.check(L.pkv_decode(shard._h, C.byref(a), out.data_ptr(), _lib.PKV_BF16, None, st))
+        launches_per_step = 2
+        grp = None
+    else:
+        from peerkv_b200.distributed import DistPeerGroup
+        grp = DistPeerGroup(dev, B, HQ, home=0)
+        shard = grp.shard
+        a = ops.make_args(q, view, my_tab, my_tab.stride(0), my_len, scale)
+
+        def step():
+            grp.step(a, q=q, out=out)
+        launches_per_step = 4 + 2 * (N - 1)
+
+    def barrier():
+        if N > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if N > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t)
+        return ms
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    if sampler:
+        sampler.start()
+    total_ms = timed(step, args.steps)
+    ms_per_step = total_ms / args.steps
+    # keep the GPU under the same load long enough for the clock sampler to see it
+    soak_steps = 0
+    if total_ms < 1500.0 and not args.lean:
+        soak_steps = int(min(20000, (1500.0 - total_ms) / max(ms_per_step, 1e-3))) + 1
+        timed(step, soak_steps)
+    clocks = sampler.stop() if sampler else None
+    status = shard.status() | (grp.xchg.status() if grp else 0)
+
+    algo_bytes = B * ctx * BYTES_PER_TOKEN
+    value = algo_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end: host buffers in, host result out, every step ------------- #
+    def e2e_step():
+        if rank == 0:
+            q.copy_(q_host, non_blocking=True)
+        my_tab.copy_(tab_host, non_blocking=True)
+        my_len.copy_(len_host, non_blocking=True)
+        step()
+        if rank == 0:
+            out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    for _ in range(3):
+        e2e_step()
+    e2e_n = 3 if args.lean else max(5, min(args.steps, 100))
+    e2e_ms = timed(e2e_step, e2e_n) / e2e_n
+    h2d = q_host.numel() * 2 + N * (tab_host.numel() * 4 + len_host.numel() * 4)
+    d2h = out_host.numel() * 2
+
+    # ---- dominant kernel alone (rank 0's shard), CUDA events around each launch ---- #
+    kern_ms = None
+    if rank == 0:
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+               for _ in range(2 if args.lean else 20)]
+        for _ in range(3):
+            _lib.check(L.pkv_decode_splits_only(shard._h, C.byref(a), st))
+        for e0, e1 in evs:
+            e0.record()
+            _lib.check(L.pkv_decode_splits_only(shard._h, C.byref(a), st))
+            e1.record()
+        torch.cuda.synchronize()
+        kern_ms = sum(e0.elapsed_time(e1) for e0, e1 in evs) / len(evs)
+    barrier()
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        kern_bytes = local_tokens * BYTES_PER_TOKEN
+        achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
+        line = {
+            "metric": "decode_attn_effective_kv_bandwidth", "value": value, "unit": "GB/s",
+            "n_gpus": N, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "us_per_layer": ms_per_step * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(N) if ctx == CTX else dict(workload_config(N), context=ctx,
+                                                                 kv_bytes_per_layer=algo_bytes),
+            "frac_of_aggregate_hbm": value / (peak * N), "frac_of_8tbs_nominal": value / (8000.0 * N),
+            "roofline": {"kernel": "decode_partial_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                         "bytes_per_launch": kern_bytes, "us_per_launch": kern_ms * 1e3,
+                         "traffic": (NCU_TRAFFIC_PER_ALGO_BYTE * kern_bytes
+                                     if NCU_TRAFFIC_PER_ALGO_BYTE else None)},
+            "e2e": {"value": algo_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "note": "q, block table and shard lengths copied from pinned host memory, result "
+                            "copied back and the stream synchronised, every step"},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": dict(clocks or {}, note=f"sampled over the timed steps plus {soak_steps} more identical steps"),
+            "device_status": status,
+        }
+        if N == 1 and not args.no_cpu_baseline and not args.lean:
+            cores = os.cpu_count() or 1
+            torch.set_num_threads(cores)
+            tokens = 131072
+            inputs = cpu_sample_inputs(tokens)
+            cpu_reference_step(inputs, 1)
+            ts = []
+            for _ in range(5):
+                t0 = time.perf_counter()
+                cpu_reference_step(inputs, 1)
+                ts.append(time.perf_counter() - t0)
+            med = sorted(ts)[len(ts) // 2]
+            line["cpu_baseline"] = {
+                "value": tokens * BYTES_PER_TOKEN / med / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+                "sample": f"1 of the 16 sequences ({tokens} tokens, 512 MiB of KV): paged gather + GQA "
+                          f"expansion + fp32 attention, median of 5 after 1 warm-up"}
+        print(json.dumps(line), flush=True)
+    if grp:
+        grp.close()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -123,6 +123,11 @@ int pkv_decode_partial(pkv_shard* s, const pkv_decode_args* a, float* o_part,
 int pkv_decode(pkv_shard* s, const pkv_decode_args* a, void* out, int32_t out_dtype,
                float* lse_out, void* stream);
 
+/* Measurement aid: launches ONLY the split-K kernel of pkv_decode (per-CTA partials
+ * stay in the shard's scratch, no combine), so its duration can be timed alone with
+ * events on `stream`.  No counterpart in the reference. */
+int pkv_decode_splits_only(pkv_shard* s, const pkv_decode_args* a, void* stream);
+
 /* Single-pass N-way LSE merge (replaces merge2_h, csrc/peer_attn_kernels.cuh:64-73,
  * and the fold of umallm/peer_parallel_attn.py:169-172).  Part i is at
  * o_parts + i*o_part_stride (floats), lse_parts + i*lse_part_stride; rows =

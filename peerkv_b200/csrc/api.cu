@@ -206,6 +206,7 @@ struct LaunchOut {
   uint64_t done_epoch = 0;
   const uint64_t* q_flag = nullptr;
   uint64_t q_epoch = 0;
+  bool skip_combine = false;
 };
 
 constexpr int kStages = 3;
@@ -268,6 +269,7 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
     PKV_CUDA(cudaGetLastError());
   }
 
+  if (lo.skip_combine) return PKV_OK;
   pkv::CombineParams c;
   memset(&c, 0, sizeof c);
   c.seq_lens = a->seq_lens;
@@ -380,6 +382,12 @@ int pkv_decode(pkv_shard* s, const pkv_decode_args* a, void* out, int32_t out_dt
   lo.out = out;
   lo.out_dtype = out_dtype;
   lo.lse_part = lse_out;
+  return launch_decode(s, a, lo, static_cast<cudaStream_t>(stream));
+}
+
+int pkv_decode_splits_only(pkv_shard* s, const pkv_decode_args* a, void* stream) {
+  LaunchOut lo;
+  lo.skip_combine = true;
   return launch_decode(s, a, lo, static_cast<cudaStream_t>(stream));
 }
 
