@@ -135,7 +135,7 @@ int build_map(pkv_shard* s, const void* base, const pkv_kv_view& kv, const CUten
   e.key = key;
   CUresult r = enc(&e.map, dt, 4, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(PKV_E_CUDA,
                 "cuTensorMapEncodeTiled failed (%d) for pool %p: heads %d page_size %d pages %lld "

@@ -12,10 +12,11 @@
 // c + seq; a sequence is therefore covered by the consecutive slots of the CTAs
 // that touched it and decode_combine_kernel merges them.
 //
-// Inside a CTA: warp 8 is the producer, 32 lanes issuing one 2 KiB TMA box each
-// per stage (K and V: 8 heads x 2 halves of the head dimension, [16 tok][64 d],
-// 128-byte swizzle so ldmatrix is bank-conflict free); warps 0..7 each own one
-// kv-head and consume the stage with tensor-core MMAs in the "swapped" form
+// Inside a CTA: warps 8 and 9 are the producers of a K ring and a V ring of 32 KiB
+// slots; 16 lanes each issue one 2 KiB TMA box per tile (8 heads x 2 halves of the
+// head dimension, [16 tok][64 d], 128-byte swizzle so ldmatrix is bank-conflict
+// free), a head's boxes completing on that head's own mbarrier.  Warps 0..7 each own
+// one kv-head and consume the tiles with tensor-core MMAs in the "swapped" form
 //     S^T[16 tok x 8 qheads] = K[16 x 128] . Q^T[128 x 8]
 //     O^T[128 d  x 8 qheads] += V^T[128 x 16] . P^T[16 x 8]
 // so the G = Hq/Hkv query heads of a group ride in the N = 8 dimension and one
@@ -32,7 +33,8 @@ constexpr int kHeadDim = 128;
 constexpr int kTileTok = 16;
 constexpr int kHeadsPerCta = 8;
 constexpr int kConsumerWarps = 8;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kProducerWarps = 2;   // one feeds the K ring, one the V ring
+constexpr int kThreads = (kConsumerWarps + kProducerWarps) * 32;
 constexpr int kMaxBatch = 4096;
 
 constexpr uint32_t kPollLimit = 1u << 22;  // polls of mbarrier.try_wait before giving up
@@ -117,11 +119,13 @@ __device__ __forceinline__ int find_seq(const int* prefix, int batch, int g) {
 
 template <int NSTAGE>
 struct SmemLayout {
-  static constexpr int kKBytes = kHeadsPerCta * kTileTok * kHeadDim * 2;  // 32 KiB
-  static constexpr int kStageBytes = 2 * kKBytes;
-  static constexpr int kDataBytes = NSTAGE * kStageBytes;
-  static constexpr int kBarOff = kDataBytes;                 // 3*NSTAGE barriers
-  static constexpr int kAbortOff = kBarOff + 3 * NSTAGE * 8;
+  static constexpr int kSlotBytes = kHeadsPerCta * kTileTok * kHeadDim * 2;  // 32 KiB: one K or V tile
+  static constexpr int kVOff = NSTAGE * kSlotBytes;                          // V ring after the K ring
+  static constexpr int kDataBytes = 2 * NSTAGE * kSlotBytes;
+  // barriers: full[ring][slot][head] then empty[ring][slot]
+  static constexpr int kBarOff = kDataBytes;
+  static constexpr int kNumBars = 2 * NSTAGE * kHeadsPerCta + 2 * NSTAGE;
+  static constexpr int kAbortOff = kBarOff + kNumBars * 8;
   static constexpr int kPrefixOff = kAbortOff + 16;
   static constexpr int kTotal = kPrefixOff + (kMaxBatch + 1) * 4 + 1024;  // +1024: manual alignment
 };
@@ -137,9 +141,13 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
   int* prefix = reinterpret_cast<int*>(sgen + L::kPrefixOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::kAbortOff);
   const uint32_t bar0 = sbase + L::kBarOff;
-  auto kfull = [&](int s) { return bar0 + 8u * s; };
-  auto vfull = [&](int s) { return bar0 + 8u * (NSTAGE + s); };
-  auto empty = [&](int s) { return bar0 + 8u * (2 * NSTAGE + s); };
+  // ring 0 = K, ring 1 = V
+  auto full = [&](int ring, int s, int h) {
+    return bar0 + 8u * ((ring * NSTAGE + s) * kHeadsPerCta + h);
+  };
+  auto empty = [&](int ring, int s) {
+    return bar0 + 8u * (2 * NSTAGE * kHeadsPerCta + ring * NSTAGE + s);
+  };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hb = blockIdx.y;                   // block of 8 kv-heads
@@ -147,11 +155,11 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
   const int heads_here = min(kHeadsPerCta, p.n_kv_heads - head0);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < NSTAGE; ++s) {
-      mbar_init(kfull(s), 1);
-      mbar_init(vfull(s), 1);
-      mbar_init(empty(s), kConsumerWarps);
-    }
+    for (int ring = 0; ring < 2; ++ring)
+      for (int s = 0; s < NSTAGE; ++s) {
+        for (int h = 0; h < kHeadsPerCta; ++h) mbar_init(full(ring, s, h), 1);
+        mbar_init(empty(ring, s), heads_here);   // one arrival per consumer warp with a head
+      }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -163,17 +171,20 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
   const int g1 = min(total, g0 + per);
   if (g0 >= g1) return;
 
-  if (warp == kConsumerWarps) {
-    // ------------------------------ producer ------------------------------ //
-    if (lane == 0) { prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v); }
-    // lane -> (K or V, head, half of the head dimension)
-    const int is_v = lane >> 4;
+  if (warp >= kConsumerWarps) {
+    // ------------------------------ producers ----------------------------- //
+    // Warp 8 feeds the K ring, warp 9 the V ring.  Lane -> (head, half of the head
+    // dimension); each lane issues one 2 KiB box per tile, and each head's two
+    // boxes complete on that head's own barrier so its consumer warp can start as
+    // soon as ITS rows have landed.
+    const int ring = warp - kConsumerWarps;
+    const CUtensorMap* map = ring ? &tm_v : &tm_k;
+    if (lane == 0) prefetch_tensormap(map);
     const int hh = (lane >> 1) & 7;
     const int dh = lane & 1;
-    const bool lane_active = hh < heads_here;
-    const uint32_t dst_off = (is_v ? L::kKBytes : 0) + hh * 4096 + dh * 2048;
-    const CUtensorMap* map = is_v ? &tm_v : &tm_k;
-    const uint32_t bytes_half = heads_here * 4096;
+    const bool lane_active = lane < 16 && hh < heads_here;
+    const uint32_t ring_base = sbase + (ring ? L::kVOff : 0);
+    const uint32_t dst_off = hh * 4096 + dh * 2048;
 
     int s = find_seq(prefix, p.batch, g0);
     int it = 0;
@@ -197,31 +208,32 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
           }
         }
         const int cnt = min(32, n - base);
+        int tpos = (ti + base) % p.tiles_per_page;
         for (int j = 0; j < cnt; ++j, ++it) {
           const int stage = it % NSTAGE;
           const uint32_t ph = (it / NSTAGE) & 1;
           const int page = __shfl_sync(0xffffffffu, my_page, j);
-          const int tok0 = ((ti + base + j) % p.tiles_per_page) * kTileTok;
-          bool got = true;
+          const int tok0 = tpos * kTileTok;
+          if (++tpos == p.tiles_per_page) tpos = 0;
+          int got = 1;
           if (lane == 0) {
-            got = false;
+            got = 0;
             for (uint32_t w = 0; w < kPollLimit; ++w) {
-              if (mbar_try_wait(empty(stage), ph ^ 1)) { got = true; break; }
+              if (mbar_try_wait(empty(ring, stage), ph ^ 1)) { got = 1; break; }
               if (*abort_flag) break;
             }
-            if (got) {
-              mbar_arrive_expect_tx(kfull(stage), bytes_half);
-              mbar_arrive_expect_tx(vfull(stage), bytes_half);
-            } else {
+            if (!got) {
               atomicOr(p.status, kStPipeTimeout);
               *abort_flag = 1;
             }
           }
-          got = __shfl_sync(0xffffffffu, (int)got, 0) != 0;
+          got = __shfl_sync(0xffffffffu, got, 0);
           if (!got) { ok = false; break; }
           if (lane_active) {
-            const uint32_t dst = sbase + stage * L::kStageBytes + dst_off;
-            const uint32_t bar = is_v ? vfull(stage) : kfull(stage);
+            const uint32_t bar = full(ring, stage, hh);
+            if (dh == 0) mbar_arrive_expect_tx(bar, 4096);
+            __syncwarp(0x0000ffffu >> (2 * (kHeadsPerCta - heads_here)));
+            const uint32_t dst = ring_base + stage * L::kSlotBytes + dst_off;
             if (p.head_major) tma_load_4d(dst, map, bar, dh * 64, tok0, head0 + hh, page);
             else              tma_load_4d(dst, map, bar, dh * 64, head0 + hh, tok0, page);
           }
@@ -232,13 +244,10 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
     if (!ok) {
       // Give copies already in flight a bounded chance to land before the CTA
       // (and its shared memory) goes away.
-      if (lane == 0) {
+      if (lane_active && dh == 0) {
         for (int back = 1; back <= NSTAGE && back <= it; ++back) {
           const int jt = it - back;
-          const int stage = jt % NSTAGE;
-          const uint32_t ph = (jt / NSTAGE) & 1;
-          mbar_wait_bounded(kfull(stage), ph, kPollLimit);
-          mbar_wait_bounded(vfull(stage), ph, kPollLimit);
+          mbar_wait_bounded(full(ring, jt % NSTAGE, hh), (jt / NSTAGE) & 1, kPollLimit);
         }
       }
     }
@@ -247,12 +256,13 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
 
   // -------------------------------- consumers -------------------------------- //
   const int hh = warp;                          // kv-head inside the block of 8
-  const bool active = hh < heads_here;
+  if (hh >= heads_here) return;                 // no head for this warp in a partial block
+  const bool active = true;
   const int kvh = head0 + hh;
   const int g = lane >> 2, t = lane & 3;        // MMA fragment row / column-pair ids
   const int G = p.group;
   const uint32_t koff = hh * 4096;
-  const uint32_t voff = L::kKBytes + hh * 4096;
+  const uint32_t voff = L::kVOff + hh * 4096;
   // ldmatrix lane addressing (row inside the [16 tok][64 d] swizzled block)
   const int krow = lane & 15, kcsel = lane >> 4;
   const int vrow = (lane & 7) + ((lane >> 4) << 3), vcsel = (lane >> 3) & 1;
@@ -314,12 +324,12 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       const int pj = ti / p.tiles_per_page;
       const int tok0 = (ti - pj * p.tiles_per_page) * kTileTok;
       const int valid = min(kTileTok, min(p.page_size - tok0, len - pj * p.page_size - tok0));
-      const uint32_t sk = sbase + stage * L::kStageBytes + koff;
-      const uint32_t sv = sbase + stage * L::kStageBytes + voff;
+      const uint32_t sk = sbase + stage * L::kSlotBytes + koff;
+      const uint32_t sv = sbase + stage * L::kSlotBytes + voff;
 
       bool got = false;
       for (uint32_t w = 0; w < kPollLimit; ++w) {
-        if (mbar_try_wait(kfull(stage), ph)) { got = true; break; }
+        if (mbar_try_wait(full(0, stage, hh), ph)) { got = true; break; }
         if (*abort_flag) break;
       }
       if (!got) { if (lane == 0) { atomicOr(p.status, kStPipeTimeout); *abort_flag = 1; } return; }
@@ -363,9 +373,13 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
         }
       }
 
+      // the K tile is now in registers (scores): hand its slot back before the PV half
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty(0, stage));
+
       got = false;
       for (uint32_t w = 0; w < kPollLimit; ++w) {
-        if (mbar_try_wait(vfull(stage), ph)) { got = true; break; }
+        if (mbar_try_wait(full(1, stage, hh), ph)) { got = true; break; }
         if (*abort_flag) break;
       }
       if (!got) { if (lane == 0) { atomicOr(p.status, kStPipeTimeout); *abort_flag = 1; } return; }
@@ -391,7 +405,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(empty(stage));
+      if (lane == 0) mbar_arrive(empty(1, stage));
     }
 
     // flush this (CTA, sequence) partial
