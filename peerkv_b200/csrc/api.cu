@@ -287,6 +287,7 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   c.done_counter = s->done_counter;
   c.done_flag = lo.done_flag;
   c.done_epoch = lo.done_epoch;
+  c.status = s->status;
   dim3 cgrid(a->batch, (a->n_q_heads + pkv::kCombineHeads - 1) / pkv::kCombineHeads);
   pkv::decode_combine_kernel<<<cgrid, 128 * pkv::kCombineHeads, (a->batch + 1) * sizeof(int), st>>>(c);
   PKV_CUDA(cudaGetLastError());

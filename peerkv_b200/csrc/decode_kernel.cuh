@@ -455,6 +455,7 @@ struct CombineParams {
   unsigned int* done_counter;  // local, zero between launches
   uint64_t* done_flag;         // may live on another GPU
   uint64_t done_epoch;
+  const uint32_t* status;      // this shard's status word: no signal after a timed-out wait
 };
 
 __device__ __forceinline__ void store_out(void* out, int dtype, int64_t idx, float v) {
@@ -508,8 +509,14 @@ decode_combine_kernel(const CombineParams p) {
       const unsigned int prev = atomicAdd(p.done_counter, 1u);
       if (prev == nblk - 1) {
         *p.done_counter = 0;
-        __threadfence_system();
-        st_release_sys_u64(p.done_flag, p.done_epoch);
+        // A partial computed without its query (or from a stalled pipeline) is not
+        // announced: the home GPU's merge then reports the missing partial itself.
+        const uint32_t bad = *reinterpret_cast<const volatile uint32_t*>(p.status) &
+                             (kStPipeTimeout | kStQTimeout);
+        if (!bad) {
+          __threadfence_system();
+          st_release_sys_u64(p.done_flag, p.done_epoch);
+        }
       }
     }
   }

@@ -50,7 +50,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 }
 
 // 4-D tiled TMA load global -> shared, completion counted in bytes on `bar`.
-// No multicast: the destination is this CTA's own shared memory.
+// The destination is this CTA's own shared memory only.
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int c0, int c1, int c2, int c3) {
   asm volatile(
