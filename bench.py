@@ -253,7 +253,7 @@ def main():
 
         def step():
             _lib.check(L.pkv_decode(shard._h, C.byref(a), out.data_ptr(), _lib.PKV_BF16, None, st))
-        launches_per_step = 2
+        launches_per_step = 1
         grp = None
     else:
         from peerkv_b200.distributed import DistPeerGroup
@@ -263,7 +263,7 @@ def main():
 
         def step():
             grp.step(a, q=q, out=out)
-        launches_per_step = 4 + 2 * (N - 1)
+        launches_per_step = 3 + (N - 1)
 
     def barrier():
         if N > 1:

@@ -91,6 +91,8 @@ struct pkv_shard {
   float* part_ml = nullptr;
   uint32_t* status = nullptr;       // device word
   unsigned int* done_counter = nullptr;
+  unsigned int* counters = nullptr;  // [n_counter_words]: 64 global words, then per (sequence, kv-head)
+  size_t n_counter_words = 0;
   std::vector<MapEntry> maps;
   uint64_t stamp = 0;
   bool attr_set = false;
@@ -252,6 +254,15 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   p.q_flag = lo.q_flag;
   p.q_epoch = lo.q_epoch;
   p.q_timeout_ns = kWaitNs;
+  p.fuse = lo.skip_combine ? 0 : 1;
+  p.out = lo.out;
+  p.out_dtype = lo.out_dtype;
+  p.o_part = lo.o_part;
+  p.lse_part = lo.lse_part;
+  p.seq_counter = s->counters + 64;
+  p.all_counter = s->counters;
+  p.done_flag = lo.done_flag;
+  p.done_epoch = lo.done_epoch;
 
   if (kv.n_pages > 0) {
     const CUtensorMap *mk = nullptr, *mv = nullptr;
@@ -267,8 +278,10 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
     else
       pkv::decode_partial_kernel<false, kStages><<<grid, block, L::kTotal, st>>>(tk, tv, p);
     PKV_CUDA(cudaGetLastError());
+    return PKV_OK;   // the combine is fused into the kernel's tail
   }
 
+  // An empty pool: only the neutral rows (O = 0, lse = -inf) and the completion flag.
   if (lo.skip_combine) return PKV_OK;
   pkv::CombineParams c;
   memset(&c, 0, sizeof c);
@@ -341,6 +354,10 @@ int pkv_shard_create(pkv_shard** out, int device, int max_batch, int n_q_heads) 
   if (e == cudaSuccess) e = cudaMalloc(&s->part_ml, ml_bytes);
   if (e == cudaSuccess) e = cudaMalloc(&s->status, 256);
   if (e == cudaSuccess) e = cudaMemset(s->status, 0, 256);
+  s->n_counter_words = (size_t)n_q_heads * max_batch + 64;   // n_kv_heads <= n_q_heads
+  if (e == cudaSuccess) e = cudaMalloc(&s->counters, s->n_counter_words * sizeof(unsigned int));
+  if (e == cudaSuccess) e = cudaMemset(s->counters, 0, s->n_counter_words * sizeof(unsigned int));
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
     pkv_shard_destroy(s);
     return fail(PKV_E_CUDA, "scratch allocation failed: %s", cudaGetErrorString(e));
@@ -356,13 +373,26 @@ int pkv_shard_destroy(pkv_shard* s) {
   cudaFree(s->part_o);
   cudaFree(s->part_ml);
   cudaFree(s->status);
+  cudaFree(s->counters);
   delete s;
   return PKV_OK;
 }
 
 int pkv_shard_status(pkv_shard* s, void* stream, uint32_t* status_out) {
   if (!s) return fail(PKV_E_INVALID, "null shard");
-  return read_status(s->device, s->status, static_cast<cudaStream_t>(stream), status_out);
+  uint32_t v = 0;
+  int rc = read_status(s->device, s->status, static_cast<cudaStream_t>(stream), &v);
+  if (rc) return rc;
+  if (v) {
+    // a wait gave up mid-kernel: the arrival counters may be left half-counted
+    DeviceGuard guard(s->device);
+    PKV_CUDA(cudaMemsetAsync(s->counters, 0, s->n_counter_words * sizeof(unsigned int),
+                             static_cast<cudaStream_t>(stream)));
+    PKV_CUDA(cudaMemsetAsync(s->done_counter, 0, sizeof(unsigned int), static_cast<cudaStream_t>(stream)));
+    PKV_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  }
+  if (status_out) *status_out = v;
+  return PKV_OK;
 }
 
 int pkv_decode_partial(pkv_shard* s, const pkv_decode_args* a, float* o_part, float* lse_part,

@@ -37,7 +37,7 @@ constexpr int kProducerWarps = 2;   // one feeds the K ring, one the V ring
 constexpr int kThreads = (kConsumerWarps + kProducerWarps) * 32;
 constexpr int kMaxBatch = 4096;
 
-constexpr uint32_t kPollLimit = 1u << 22;  // polls of mbarrier.try_wait before giving up
+constexpr uint32_t kPollLimit = 1u << 20;  // polls of mbarrier.try_wait before giving up
 
 enum : uint32_t {
   kStPipeTimeout = 0x1u,
@@ -69,6 +69,16 @@ struct DecodeParams {
   const uint64_t* q_flag;  // null, or: wait until *q_flag >= q_epoch before reading q
   uint64_t q_epoch;
   uint64_t q_timeout_ns;
+  // fused combine: the last CTA to finish a sequence merges that sequence's slots
+  int fuse;                    // 0: leave the per-CTA partials in part_o / part_ml
+  int out_dtype;               // 0 f16, 1 bf16, 4 f32
+  void* out;                   // [B][Hq][128] final output, or null
+  float* o_part;               // [B][Hq][128] f32 normalised shard partial, or null (may be P2P)
+  float* lse_part;             // [B][Hq] natural log, or null (may be P2P)
+  unsigned int* seq_counter;   // [batch][n_kv_heads], zero between launches
+  unsigned int* all_counter;   // sequences finished, zero between launches
+  uint64_t* done_flag;         // released with done_epoch when every sequence is out (may be P2P)
+  uint64_t done_epoch;
 };
 
 // Tiles of a sequence with `len` tokens in this shard.
@@ -115,6 +125,111 @@ __device__ __forceinline__ int find_seq(const int* prefix, int batch, int g) {
     if (prefix[mid] <= g) lo = mid; else hi = mid;
   }
   return lo;
+}
+
+__device__ __forceinline__ void store_out(void* out, int dtype, int64_t idx, float v) {
+  if (dtype == 4) reinterpret_cast<float*>(out)[idx] = v;
+  else if (dtype == 1) reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
+  else reinterpret_cast<__half*>(out)[idx] = __float2half_rn(v);
+}
+
+__device__ __forceinline__ void store_out4(void* out, int dtype, int64_t idx, float4 v) {
+  if (dtype == 4) {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + idx) = v;
+  } else if (dtype == 1) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + idx) =
+        make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+  } else {
+    __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(out) + idx) =
+        make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+  }
+}
+
+// One warp merges the per-CTA partial slots c0..c1 of sequence b for up to four query
+// heads qh0.. and writes their rows; each lane owns 4 of the 128 dims.  c1 < c0 means
+// the shard holds no token of the sequence.  This runs in the kernel's tail, where a
+// dependent chain of L2 round trips is what costs, so each step first issues all
+// loads of four slots x four heads (statistics and rows, none depending on another
+// and no shuffle in between) and only then does the arithmetic.
+__device__ __forceinline__ void combine_heads4(const DecodeParams& p, int b, int qh0, int nh,
+                                               int c0, int c1, int lane) {
+  float4 acc[4];
+  float M[4], L[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    M[i] = -INFINITY; L[i] = 0.f;
+  }
+  const float2* ml2 = reinterpret_cast<const float2*>(p.part_ml);
+  for (int base = c0; base <= c1; base += 4) {
+    float2 ml[4][4];
+    float4 os[4][4];
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      const int c = min(base + jj, c1);           // clamped: a valid row even past the end
+      const int64_t row0 = (int64_t)(c + b) * p.n_q_heads + qh0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int64_t row = row0 + (i < nh ? i : 0);
+        ml[jj][i] = __ldcg(ml2 + row);
+        os[jj][i] = __ldcg(reinterpret_cast<const float4*>(p.part_o + row * kHeadDim) + lane);
+      }
+    }
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      if (base + jj <= c1) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float mn = fmaxf(M[i], ml[jj][i].x);
+          const float ca = fast_exp2(M[i] - mn), cs = fast_exp2(ml[jj][i].x - mn);
+          L[i] = L[i] * ca + ml[jj][i].y * cs;
+          acc[i].x = acc[i].x * ca + os[jj][i].x * cs; acc[i].y = acc[i].y * ca + os[jj][i].y * cs;
+          acc[i].z = acc[i].z * ca + os[jj][i].z * cs; acc[i].w = acc[i].w * ca + os[jj][i].w * cs;
+          M[i] = mn;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (i < nh) {
+      const float inv = L[i] > 0.f ? 1.f / L[i] : 0.f;
+      float4 v = acc[i];
+      v.x *= inv; v.y *= inv; v.z *= inv; v.w *= inv;
+      const int64_t idx = ((int64_t)b * p.n_q_heads + qh0 + i) * kHeadDim + lane * 4;
+      if (p.out) store_out4(p.out, p.out_dtype, idx, v);
+      if (p.o_part) *reinterpret_cast<float4*>(p.o_part + idx) = v;
+      if (p.lse_part && lane == 0)
+        p.lse_part[(int64_t)b * p.n_q_heads + qh0 + i] =
+            L[i] > 0.f ? (M[i] + log2f(L[i])) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+}
+
+__device__ __forceinline__ void combine_group(const DecodeParams& p, int b, int qh0, int nq,
+                                              int c0, int c1, int lane) {
+  combine_heads4(p, b, qh0, min(nq, 4), c0, c1, lane);
+  if (nq > 4) combine_heads4(p, b, qh0 + 4, nq - 4, c0, c1, lane);
+}
+
+// Counts `n` finished (sequence, kv-head) units; whoever completes the count
+// re-arms the counter and releases the completion flag (unless a wait timed out).
+__device__ __forceinline__ void count_done(const DecodeParams& p, unsigned int n,
+                                           unsigned int expected) {
+  const unsigned int prev = atomicAdd(p.all_counter, n);
+  if (prev + n == expected) {
+    *p.all_counter = 0;
+    if (p.done_flag) {
+      const uint32_t bad = *reinterpret_cast<const volatile uint32_t*>(p.status) &
+                           (kStPipeTimeout | kStQTimeout);
+      if (!bad) {
+        __threadfence_system();
+        st_release_sys_u64(p.done_flag, p.done_epoch);
+      }
+    }
+  }
 }
 
 template <int NSTAGE>
@@ -169,6 +284,23 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
   const int per = (total + p.n_cta_x - 1) / p.n_cta_x;
   const int g0 = min(total, (int)blockIdx.x * per);
   const int g1 = min(total, g0 + per);
+  const unsigned int units = (unsigned int)p.batch * p.n_kv_heads;   // (sequence, kv-head) pairs
+
+  if (p.fuse && blockIdx.x == 0) {
+    // Sequences with no tokens in this shard have no CTA: write their neutral rows here.
+    const int qh0 = head0 * p.group, nqh = heads_here * p.group;
+    int n_empty = 0;
+    for (int b = 0; b < p.batch; ++b) {
+      if (prefix[b + 1] != prefix[b]) continue;
+      ++n_empty;
+      for (int i = warp; i < nqh; i += kThreads / 32) combine_group(p, b, qh0 + i, 1, 0, -1, lane);
+    }
+    if (n_empty && p.done_flag) {
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x == 0) count_done(p, n_empty * heads_here, units);
+    }
+  }
   if (g0 >= g1) return;
 
   if (warp >= kConsumerWarps) {
@@ -435,6 +567,33 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
         if (h1 < G) { p.part_ml[(hbase + h1) * 2] = m1; p.part_ml[(hbase + h1) * 2 + 1] = l1; }
       }
     }
+
+    if (p.fuse) {
+      // Each consumer warp is on its own: it counts its (sequence, kv-head) in, and
+      // the warp that arrives last for that pair merges the pair's slots.  No
+      // CTA-wide meeting, so the other warps run straight into the next sequence.
+      const int t0s = prefix[s], t1s = prefix[s + 1];
+      const int c0 = t0s / per, c1 = (t1s - 1) / per;
+      __threadfence();
+      __syncwarp();
+      int last = 0;
+      if (lane == 0) {
+        unsigned int* ctr = p.seq_counter + (size_t)s * p.n_kv_heads + kvh;
+        const unsigned int prev = atomicAdd(ctr, 1u);
+        last = prev == (unsigned int)(c1 - c0);
+        if (last) *ctr = 0;
+        __threadfence();
+      }
+      last = __shfl_sync(0xffffffffu, last, 0);
+      if (last) {
+        combine_group(p, s, kvh * G, G, c0, c1, lane);
+        if (p.done_flag) {
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0) count_done(p, 1u, units);
+        }
+      }
+    }
   }
 }
 
@@ -458,11 +617,6 @@ struct CombineParams {
   const uint32_t* status;      // this shard's status word: no signal after a timed-out wait
 };
 
-__device__ __forceinline__ void store_out(void* out, int dtype, int64_t idx, float v) {
-  if (dtype == 4) reinterpret_cast<float*>(out)[idx] = v;
-  else if (dtype == 1) reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
-  else reinterpret_cast<__half*>(out)[idx] = __float2half_rn(v);
-}
 
 constexpr int kCombineHeads = 4;  // q heads per combine block (one warp-quad of 128 threads each)
 
