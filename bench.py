@@ -263,7 +263,7 @@ def main():
 
         def step():
             grp.step(a, q=q, out=out)
-        launches_per_step = 3 + (N - 1)
+        launches_per_step = N + 1      # one kernel per GPU per step, plus the q publish on GPU 0
 
     def barrier():
         if N > 1:

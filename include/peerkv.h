@@ -190,6 +190,14 @@ int pkv_home_publish_q(pkv_exchange* x, const void* q, int32_t batch, void* stre
  * a->q is ignored unless q_override != 0. */
 int pkv_peer_step(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, int32_t home_rank,
                   int32_t q_override, void* stream);
+/* Home rank, one whole step in two launches: pkv_home_publish_q, then ONE kernel that
+ * streams the home shard, combines its splits and, in its tail, waits (bounded,
+ * device side) for the flags of the ranks in wait_mask and folds their partials in.
+ * out [batch, n_q_heads, 128] in out_dtype; lse_out may be NULL.  Same result as
+ * pkv_home_publish_q + pkv_home_partial + pkv_home_merge with one launch fewer;
+ * replaces the host orchestration of csrc/peer_fused_attn_ext.cu:94-135. */
+int pkv_home_step(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, uint32_t wait_mask,
+                  void* out, int32_t out_dtype, float* lse_out, void* stream);
 /* Home rank: its own shard's partial into its own slot (after pkv_home_publish_q). */
 int pkv_home_partial(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, void* stream);
 /* Home rank: waits (bounded, device side) for the flags of the ranks in

@@ -19,7 +19,7 @@ EXPORTS = [
     "pkv_shard_status", "pkv_decode_partial", "pkv_decode", "pkv_decode_splits_only", "pkv_merge_partials",
     "pkv_quantize_kv", "pkv_split_block_table", "pkv_exchange_create", "pkv_exchange_destroy", "pkv_exchange_export",
     "pkv_exchange_import", "pkv_exchange_attach", "pkv_exchange_status", "pkv_exchange_epoch",
-    "pkv_home_publish_q", "pkv_peer_step", "pkv_home_partial", "pkv_home_merge",
+    "pkv_home_publish_q", "pkv_home_step", "pkv_peer_step", "pkv_home_partial", "pkv_home_merge",
 ]
 
 
@@ -80,6 +80,7 @@ def lib():
         "pkv_exchange_status": [vp, vp, P(u32)],
         "pkv_exchange_epoch": [vp, P(u64)],
         "pkv_home_publish_q": [vp, vp, i32, vp],
+        "pkv_home_step": [vp, vp, P(DecodeArgs), u32, vp, i32, vp, vp],
         "pkv_peer_step": [vp, vp, P(DecodeArgs), i32, i32, vp],
         "pkv_home_partial": [vp, vp, P(DecodeArgs), vp],
         "pkv_home_merge": [vp, i32, u32, vp, i32, vp, vp],

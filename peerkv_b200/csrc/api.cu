@@ -98,6 +98,34 @@ struct pkv_shard {
   bool attr_set = false;
 };
 
+struct pkv_exchange {
+  int device = 0, rank = 0, world = 1, max_batch = 0, n_q_heads = 0;
+  uint8_t* slab = nullptr;                  // this GPU's mailboxes (cudaMalloc)
+  uint8_t* peer_slab[pkv::kMaxWorld] = {};  // mapped slabs by rank (own slab at [rank])
+  bool imported[pkv::kMaxWorld] = {};       // opened with cudaIpcOpenMemHandle
+  uint32_t* status = nullptr;               // local: status word + counters
+  uint64_t epoch = 0;
+  size_t off_q = 0, off_o = 0, off_lse = 0, off_flags = 0, slab_bytes = 0;
+  size_t o_part_elems = 0, lse_part_elems = 0;
+};
+
+namespace {
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+float* slot_o(pkv_exchange* x, int owner_rank, int slot) {
+  return reinterpret_cast<float*>(x->peer_slab[owner_rank] + x->off_o) + (size_t)slot * x->o_part_elems;
+}
+float* slot_lse(pkv_exchange* x, int owner_rank, int slot) {
+  return reinterpret_cast<float*>(x->peer_slab[owner_rank] + x->off_lse) + (size_t)slot * x->lse_part_elems;
+}
+uint64_t* flag_ptr(pkv_exchange* x, int owner_rank, int idx) {   // idx world = q flag
+  return reinterpret_cast<uint64_t*>(x->peer_slab[owner_rank] + x->off_flags) + idx;
+}
+
+}  // namespace
+
+
 namespace {
 
 int build_map(pkv_shard* s, const void* base, const pkv_kv_view& kv, const CUtensorMap** out) {
@@ -209,6 +237,8 @@ struct LaunchOut {
   const uint64_t* q_flag = nullptr;
   uint64_t q_epoch = 0;
   bool skip_combine = false;
+  pkv_exchange* home = nullptr;   // set: publish q, wait for the peers and merge in the same kernel
+  uint32_t wait_mask = 0;
 };
 
 constexpr int kStages = 3;
@@ -263,6 +293,20 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   p.all_counter = s->counters;
   p.done_flag = lo.done_flag;
   p.done_epoch = lo.done_epoch;
+  if (lo.home) {
+    pkv_exchange* x = lo.home;
+    p.mg_n = x->world;
+    p.mg_self = x->rank;
+    p.mg_wait_mask = lo.wait_mask & ~(1u << x->rank);
+    p.mg_o = slot_o(x, x->rank, 0);
+    p.mg_lse = slot_lse(x, x->rank, 0);
+    p.mg_o_stride = (int64_t)x->o_part_elems;
+    p.mg_lse_stride = (int64_t)x->lse_part_elems;
+    p.mg_flags = flag_ptr(x, x->rank, 0);
+    p.mg_epoch = x->epoch;
+    p.mg_timeout_ns = kWaitNs;
+    p.mg_status = x->status;
+  }
 
   if (kv.n_pages > 0) {
     const CUtensorMap *mk = nullptr, *mv = nullptr;
@@ -501,33 +545,6 @@ int pkv_split_block_table(int device, const int32_t* block_table, int64_t block_
 // ------------------------------------------------------------------------- //
 // several GPUs
 // ------------------------------------------------------------------------- //
-struct pkv_exchange {
-  int device = 0, rank = 0, world = 1, max_batch = 0, n_q_heads = 0;
-  uint8_t* slab = nullptr;                  // this GPU's mailboxes (cudaMalloc)
-  uint8_t* peer_slab[pkv::kMaxWorld] = {};  // mapped slabs by rank (own slab at [rank])
-  bool imported[pkv::kMaxWorld] = {};       // opened with cudaIpcOpenMemHandle
-  uint32_t* status = nullptr;               // local: status word + counters
-  uint64_t epoch = 0;
-  size_t off_q = 0, off_o = 0, off_lse = 0, off_flags = 0, slab_bytes = 0;
-  size_t o_part_elems = 0, lse_part_elems = 0;
-};
-
-namespace {
-
-size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
-
-float* slot_o(pkv_exchange* x, int owner_rank, int slot) {
-  return reinterpret_cast<float*>(x->peer_slab[owner_rank] + x->off_o) + (size_t)slot * x->o_part_elems;
-}
-float* slot_lse(pkv_exchange* x, int owner_rank, int slot) {
-  return reinterpret_cast<float*>(x->peer_slab[owner_rank] + x->off_lse) + (size_t)slot * x->lse_part_elems;
-}
-uint64_t* flag_ptr(pkv_exchange* x, int owner_rank, int idx) {   // idx world = q flag
-  return reinterpret_cast<uint64_t*>(x->peer_slab[owner_rank] + x->off_flags) + idx;
-}
-
-}  // namespace
-
 extern "C" {
 
 int pkv_exchange_create(pkv_exchange** out, int device, int rank, int world, int max_batch,
@@ -640,7 +657,6 @@ int pkv_home_publish_q(pkv_exchange* x, const void* q, int32_t batch, void* stre
   p.q = static_cast<const uint4*>(q);
   p.n16 = (int64_t)batch * x->n_q_heads * pkv::kHeadDim * 2 / 16;
   p.epoch = x->epoch;
-  p.counter = reinterpret_cast<unsigned int*>(x->status) + 32;
   int n = 0;
   for (int r = 0; r < x->world; ++r) {
     if (r == x->rank) continue;
@@ -649,13 +665,10 @@ int pkv_home_publish_q(pkv_exchange* x, const void* q, int32_t batch, void* stre
     p.flag[n] = flag_ptr(x, r, x->world);
     ++n;
   }
-  p.n_dst = n;
   if (n == 0) return PKV_OK;
   DeviceGuard guard(x->device);
   if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", x->device);
-  int bx = static_cast<int>((p.n16 + 255) / 256);
-  if (bx > 16) bx = 16;
-  pkv::publish_q_kernel<<<dim3(bx, n), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  pkv::publish_q_kernel<<<n, 1024, 0, static_cast<cudaStream_t>(stream)>>>(p);
   PKV_CUDA(cudaGetLastError());
   return PKV_OK;
 }
@@ -690,6 +703,34 @@ int pkv_home_partial(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, vo
   LaunchOut lo;
   lo.o_part = slot_o(x, x->rank, x->rank);
   lo.lse_part = slot_lse(x, x->rank, x->rank);
+  return launch_decode(s, a, lo, static_cast<cudaStream_t>(stream));
+}
+
+int pkv_home_step(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, uint32_t wait_mask,
+                  void* out, int32_t out_dtype, float* lse_out, void* stream) {
+  if (!x || !s || !a || !out) return fail(PKV_E_INVALID, "null pointer");
+  if (a->batch <= 0 || a->batch > x->max_batch) return fail(PKV_E_INVALID, "batch %d", a->batch);
+  if (a->n_q_heads != x->n_q_heads) return fail(PKV_E_INVALID, "n_q_heads mismatch");
+  if (out_dtype != PKV_F16 && out_dtype != PKV_BF16 && out_dtype != PKV_F32)
+    return fail(PKV_E_INVALID, "out_dtype %d", out_dtype);
+  if (reinterpret_cast<uintptr_t>(a->q) & 15) return fail(PKV_E_INVALID, "q must be 16-byte aligned");
+  for (int r = 0; r < x->world; ++r)
+    if (!x->peer_slab[r]) return fail(PKV_E_STATE, "rank %d is not attached", r);
+  if (a->kv.n_pages == 0) {
+    // nothing of the KV lives here: the three-kernel form covers it
+    int rc = pkv_home_publish_q(x, a->q, a->batch, stream);
+    if (!rc) rc = pkv_home_partial(x, s, a, stream);
+    if (!rc) rc = pkv_home_merge(x, a->batch, wait_mask, out, out_dtype, lse_out, stream);
+    return rc;
+  }
+  int rc = pkv_home_publish_q(x, a->q, a->batch, stream);   // bumps the epoch
+  if (rc) return rc;
+  LaunchOut lo;
+  lo.out = out;
+  lo.out_dtype = out_dtype;
+  lo.lse_part = lse_out;
+  lo.home = x;
+  lo.wait_mask = wait_mask;
   return launch_decode(s, a, lo, static_cast<cudaStream_t>(stream));
 }
 

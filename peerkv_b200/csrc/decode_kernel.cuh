@@ -34,7 +34,8 @@ constexpr int kTileTok = 16;
 constexpr int kHeadsPerCta = 8;
 constexpr int kConsumerWarps = 8;
 constexpr int kProducerWarps = 2;   // one feeds the K ring, one the V ring
-constexpr int kThreads = (kConsumerWarps + kProducerWarps) * 32;
+constexpr int kServiceWarp = kConsumerWarps + kProducerWarps;  // rows of token-less sequences
+constexpr int kThreads = (kConsumerWarps + kProducerWarps + 1) * 32;
 constexpr int kMaxBatch = 4096;
 
 constexpr uint32_t kPollLimit = 1u << 20;  // polls of mbarrier.try_wait before giving up
@@ -79,6 +80,18 @@ struct DecodeParams {
   unsigned int* all_counter;   // sequences finished, zero between launches
   uint64_t* done_flag;         // released with done_epoch when every sequence is out (may be P2P)
   uint64_t done_epoch;
+  // home GPU only -- final merge in the tail: after a (sequence, kv-head) is combined locally
+  // the same warp waits (bounded) for the peers' flags and folds their (O, lse) rows in.
+  int mg_n;                    // partial slots (ranks); 0 = no merge
+  int mg_self;                 // this rank's slot (its own rows never leave the registers)
+  uint32_t mg_wait_mask;       // bit r: wait for mg_flags[r] >= mg_epoch
+  const float* mg_o;           // slot r at mg_o + r * mg_o_stride: [B][Hq][128]
+  const float* mg_lse;         // slot r at mg_lse + r * mg_lse_stride: [B][Hq]
+  int64_t mg_o_stride, mg_lse_stride;
+  const uint64_t* mg_flags;
+  uint64_t mg_epoch;
+  uint64_t mg_timeout_ns;
+  uint32_t* mg_status;         // the exchange's status word
 };
 
 // Tiles of a sequence with `len` tokens in this shard.
@@ -147,6 +160,19 @@ __device__ __forceinline__ void store_out4(void* out, int dtype, int64_t idx, fl
   }
 }
 
+// Online-softmax fold of one slot (running max m in log2 units, sum l, unnormalised row o)
+// into the accumulator; a slot with m = -inf carries no tokens and is skipped.
+__device__ __forceinline__ void fold_slot(float& M, float& L, float4& acc, float m, float l,
+                                          const float4& o) {
+  if (m == -INFINITY) return;
+  const float mn = fmaxf(M, m);
+  const float ca = fast_exp2(M - mn), cs = fast_exp2(m - mn);
+  L = L * ca + l * cs;
+  acc.x = acc.x * ca + o.x * cs; acc.y = acc.y * ca + o.y * cs;
+  acc.z = acc.z * ca + o.z * cs; acc.w = acc.w * ca + o.w * cs;
+  M = mn;
+}
+
 // One warp merges the per-CTA partial slots c0..c1 of sequence b for up to four query
 // heads qh0.. and writes their rows; each lane owns 4 of the 128 dims.  c1 < c0 means
 // the shard holds no token of the sequence.  This runs in the kernel's tail, where a
@@ -181,14 +207,30 @@ __device__ __forceinline__ void combine_heads4(const DecodeParams& p, int b, int
     for (int jj = 0; jj < 4; ++jj) {
       if (base + jj <= c1) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float mn = fmaxf(M[i], ml[jj][i].x);
-          const float ca = fast_exp2(M[i] - mn), cs = fast_exp2(ml[jj][i].x - mn);
-          L[i] = L[i] * ca + ml[jj][i].y * cs;
-          acc[i].x = acc[i].x * ca + os[jj][i].x * cs; acc[i].y = acc[i].y * ca + os[jj][i].y * cs;
-          acc[i].z = acc[i].z * ca + os[jj][i].z * cs; acc[i].w = acc[i].w * ca + os[jj][i].w * cs;
-          M[i] = mn;
-        }
+        for (int i = 0; i < 4; ++i) fold_slot(M[i], L[i], acc[i], ml[jj][i].x, ml[jj][i].y, os[jj][i]);
+      }
+    }
+  }
+  // The peers' shard partials are slots too: (m = lse * log2 e, l = 1, o = O normalised).
+  for (int r0 = 0; r0 < p.mg_n; r0 += 4) {
+    float ls[4][4];
+    float4 os[4][4];
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      const int r = min(r0 + jj, p.mg_n - 1);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int64_t row = (int64_t)b * p.n_q_heads + qh0 + (i < nh ? i : 0);
+        ls[jj][i] = __ldcg(p.mg_lse + r * p.mg_lse_stride + row);
+        os[jj][i] = __ldcg(reinterpret_cast<const float4*>(p.mg_o + r * p.mg_o_stride + row * kHeadDim) + lane);
+      }
+    }
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      if (r0 + jj < p.mg_n && r0 + jj != p.mg_self) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          fold_slot(M[i], L[i], acc[i], ls[jj][i] * 1.4426950408889634f, 1.f, os[jj][i]);
       }
     }
   }
@@ -212,6 +254,24 @@ __device__ __forceinline__ void combine_group(const DecodeParams& p, int b, int 
                                               int c0, int c1, int lane) {
   combine_heads4(p, b, qh0, min(nq, 4), c0, c1, lane);
   if (nq > 4) combine_heads4(p, b, qh0 + 4, nq - 4, c0, c1, lane);
+}
+
+// Bounded wait of one warp for the peers' completion flags (lane r polls rank r).
+// Returns false, with the status bit set, if a flag did not reach the epoch in time.
+__device__ __forceinline__ bool wait_peer_flags(const DecodeParams& p, int lane) {
+  bool ok = true;
+  if (lane < p.mg_n && ((p.mg_wait_mask >> lane) & 1u)) {
+    uint64_t t0, now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+      if (ld_acquire_sys_u64(p.mg_flags + lane) >= p.mg_epoch) break;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (now - t0 > p.mg_timeout_ns) { ok = false; break; }
+      __nanosleep(64);
+    }
+    if (!ok) atomicOr(p.mg_status, kStPartialTimeout);
+  }
+  return __all_sync(0xffffffffu, ok);
 }
 
 // Counts `n` finished (sequence, kv-head) units; whoever completes the count
@@ -286,24 +346,32 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
   const int g1 = min(total, g0 + per);
   const unsigned int units = (unsigned int)p.batch * p.n_kv_heads;   // (sequence, kv-head) pairs
 
-  if (p.fuse && blockIdx.x == 0) {
-    // Sequences with no tokens in this shard have no CTA: write their neutral rows here.
-    const int qh0 = head0 * p.group, nqh = heads_here * p.group;
-    int n_empty = 0;
-    for (int b = 0; b < p.batch; ++b) {
-      if (prefix[b + 1] != prefix[b]) continue;
-      ++n_empty;
-      for (int i = warp; i < nqh; i += kThreads / 32) combine_group(p, b, qh0 + i, 1, 0, -1, lane);
+  if (warp == kServiceWarp) {
+    // ---------------------------- service warp ---------------------------- //
+    // Sequences with no token in this shard have no CTA: CTA 0 of each head block
+    // writes their rows (neutral, or the merge of the peers' rows on the home GPU).
+    if (p.fuse && blockIdx.x == 0) {
+      const int qh0 = head0 * p.group, nqh = heads_here * p.group;
+      int n_empty = 0;
+      bool peers_ok = true, waited = false;
+      for (int b = 0; b < p.batch; ++b) {
+        if (prefix[b + 1] != prefix[b]) continue;
+        ++n_empty;
+        if (p.mg_n > 0 && !waited) { peers_ok = wait_peer_flags(p, lane); waited = true; }
+        if (peers_ok)
+          for (int i = 0; i < nqh; i += 4) combine_heads4(p, b, qh0 + i, min(4, nqh - i), 0, -1, lane);
+      }
+      if (n_empty && p.done_flag) {
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) count_done(p, n_empty * heads_here, units);
+      }
     }
-    if (n_empty && p.done_flag) {
-      __threadfence_system();
-      __syncthreads();
-      if (threadIdx.x == 0) count_done(p, n_empty * heads_here, units);
-    }
+    return;
   }
   if (g0 >= g1) return;
 
-  if (warp >= kConsumerWarps) {
+  if (warp >= kConsumerWarps) {   // warps 8, 9 (the service warp has returned)
     // ------------------------------ producers ----------------------------- //
     // Warp 8 feeds the K ring, warp 9 the V ring.  Lane -> (head, half of the head
     // dimension); each lane issues one 2 KiB box per tile, and each head's two
@@ -585,6 +653,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
         __threadfence();
       }
       last = __shfl_sync(0xffffffffu, last, 0);
+      if (last && p.mg_n > 0) last = wait_peer_flags(p, lane) ? 1 : 0;   // home: peers' rows needed
       if (last) {
         combine_group(p, s, kvh * G, G, c0, c1, lane);
         if (p.done_flag) {

@@ -12,30 +12,33 @@ constexpr int kMaxWorld = 16;
 struct PublishParams {
   const uint4* q;          // [n16] 16-byte words of q
   int64_t n16;
-  int n_dst;
-  uint4* dst[kMaxWorld];   // peers' q inboxes (P2P mapped)
+  uint4* dst[kMaxWorld];   // peers' q inboxes (P2P mapped), one block per peer
   uint64_t* flag[kMaxWorld];
   uint64_t epoch;
-  unsigned int* counter;   // local, zero between launches
 };
 
-// grid.y = destination peer, grid.x blocks stride over q.  The last block of each
-// destination releases that peer's q flag.
-__global__ void __launch_bounds__(256) publish_q_kernel(const PublishParams p) {
-  const int dsti = blockIdx.y;
-  uint4* dst = p.dst[dsti];
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.n16;
-       i += (int64_t)gridDim.x * blockDim.x)
-    dst[i] = p.q[i];
-  __threadfence_system();
+// One 1024-thread block per destination peer: all loads first, then the P2P stores,
+// one block barrier, and a single system-scope release of that peer's q flag (the
+// barrier makes the release cumulative over the whole block's stores).
+__global__ void __launch_bounds__(1024) publish_q_kernel(const PublishParams p) {
+  uint4* dst = p.dst[blockIdx.x];
+  for (int64_t i0 = 0; i0 < p.n16; i0 += 4096) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t i = i0 + threadIdx.x + 1024 * u;
+      if (i < p.n16) v[u] = __ldcg(p.q + i);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t i = i0 + threadIdx.x + 1024 * u;
+      if (i < p.n16) dst[i] = v[u];
+    }
+  }
   __syncthreads();
   if (threadIdx.x == 0) {
-    const unsigned int prev = atomicAdd(p.counter + dsti, 1u);
-    if (prev == gridDim.x - 1) {
-      p.counter[dsti] = 0;
-      __threadfence_system();
-      st_release_sys_u64(p.flag[dsti], p.epoch);
-    }
+    __threadfence_system();
+    st_release_sys_u64(p.flag[blockIdx.x], p.epoch);
   }
 }
 

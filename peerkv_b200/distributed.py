@@ -52,10 +52,10 @@ class DistPeerGroup:
         st = ops._stream(self.device)
         if self.is_home:
             B = args.batch
-            check(L.pkv_home_publish_q(self.xchg._h, q.data_ptr(), B, st))
-            check(L.pkv_home_partial(self.xchg._h, self.shard._h, C.byref(args), st))
             mask = ((1 << self.world) - 1) & ~(1 << self.rank)
-            check(L.pkv_home_merge(self.xchg._h, B, mask, out.data_ptr(), ops._DT[out.dtype], None, st))
+            args.q = q.data_ptr()
+            check(L.pkv_home_step(self.xchg._h, self.shard._h, C.byref(args), mask, out.data_ptr(),
+                                  ops._DT[out.dtype], None, st))
             return out
         check(L.pkv_peer_step(self.xchg._h, self.shard._h, C.byref(args), self.home, 0, st))
         return None

@@ -4,11 +4,12 @@ on cuda:0 and cuda:1, PeerKV csrc/peer_fused_attn_ext.cu:37-137).
 A PeerGroup owns, per GPU, a Shard (split-K scratch) and an Exchange (mailboxes)
 created once and mapped into each other with peer access.  A step is:
 
-    home:  publish q -> peers (P2P stores + flag)        pkv_home_publish_q
-    peers: partial over their shard, pushed into the     pkv_peer_step
-           home GPU's slot (P2P stores + flag)
-    home:  own partial, then one merge that waits on     pkv_home_partial
-           the peers' flags                              pkv_home_merge
+    peers: one kernel each -- wait for q, partial over    pkv_peer_step
+           their shard, push it into the home GPU's slot
+           (P2P stores + flag)
+    home:  push q to the peers (P2P stores + flag), then  pkv_home_step
+           one kernel -- partial over its own shard, wait
+           for the peers' flags, merge
 
 No stream, event or scratch is created per call and the host never blocks.
 Calls on one group must come from one thread and, per GPU, one stream.
@@ -108,7 +109,6 @@ class PeerGroup:
         home = self.devices[0]
         B = q.shape[0]
         hs = ops._stream(home)
-        check(L.pkv_home_publish_q(self.xchg[0]._h, q.data_ptr(), B, hs))
         mask = 0
         for r in range(1, self.world):
             d = self.devices[r]
@@ -119,8 +119,8 @@ class PeerGroup:
                 check(L.pkv_peer_step(self.xchg[r]._h, self.shards[r]._h, C.byref(args[r]), 0, 0,
                                       st.cuda_stream))
             mask |= 1 << r
-        check(L.pkv_home_partial(self.xchg[0]._h, self.shards[0]._h, C.byref(args[0]), hs))
-        check(L.pkv_home_merge(self.xchg[0]._h, B, mask, out.data_ptr(), ops._DT[out.dtype], None, hs))
+        check(L.pkv_home_step(self.xchg[0]._h, self.shards[0]._h, C.byref(args[0]), mask,
+                              out.data_ptr(), ops._DT[out.dtype], None, hs))
         return out
 
     def decode_contiguous(self, q: torch.Tensor, shards: List[Tuple[torch.Tensor, torch.Tensor]],
