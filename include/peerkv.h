@@ -123,6 +123,31 @@ int pkv_decode_partial(pkv_shard* s, const pkv_decode_args* a, float* o_part,
 int pkv_decode(pkv_shard* s, const pkv_decode_args* a, void* out, int32_t out_dtype,
                float* lse_out, void* stream);
 
+/* pkv_decode for callers that must not allocate device memory.  No counterpart in the
+ * reference (its op allocates fresh scratch tensors on every call).
+ *
+ * Some hosts of this library cannot call cudaMalloc at the point where they need
+ * attention: a plugin running inside another runtime's memory pool whose budget is
+ * already fully handed out, a serving process that pre-sizes all GPU memory at start-up
+ * and treats any later allocation as a fault, or code on a path where the allocator's
+ * implicit device synchronisation is not acceptable.  For them the split-K scratch
+ * lives in arrays that are part of the library image itself: about 7.4 MB per GPU, held
+ * by every GPU that loads the library until the process ends.
+ *
+ * Same arguments and result as pkv_decode, minus the shard object.  Limits, checked
+ * with a clear error: at most 32 sequences and 64 query heads per call (and a GPU of
+ * at most 192 SMs).  The call makes no cudaMalloc / cudaFree and uses no allocating
+ * library routine; the caller still owns q, the KV pool, tables and outputs.
+ *
+ * The first call on a device does the one-time set-up for that device (looks up the
+ * arrays' device addresses, raises the kernel's shared-memory limit), so make it
+ * before starting any stream capture.  All calls on a device share the one scratch:
+ * each call first clears the words that must start at zero, and two calls whose
+ * kernels overlap on the GPU (different streams, no ordering between them) race on
+ * it -- order them, or use pkv_decode with separate shards. */
+int pkv_decode_static(int device, const pkv_decode_args* a, void* out, int32_t out_dtype,
+                      float* lse_out, void* stream);
+
 /* Measurement aid: launches ONLY the split-K kernel of pkv_decode (per-CTA partials
  * stay in the shard's scratch, no combine), so its duration can be timed alone with
  * events on `stream`.  No counterpart in the reference. */

@@ -16,7 +16,7 @@ ST_PIPE_TIMEOUT, ST_BAD_PAGE, ST_Q_TIMEOUT, ST_PARTIAL_TIMEOUT = 1, 2, 4, 8
 
 EXPORTS = [
     "pkv_last_error", "pkv_abi_version", "pkv_shard_create", "pkv_shard_destroy",
-    "pkv_shard_status", "pkv_decode_partial", "pkv_decode", "pkv_decode_splits_only", "pkv_merge_partials",
+    "pkv_shard_status", "pkv_decode_partial", "pkv_decode", "pkv_decode_static", "pkv_decode_splits_only", "pkv_merge_partials",
     "pkv_quantize_kv", "pkv_split_block_table", "pkv_exchange_create", "pkv_exchange_destroy", "pkv_exchange_export",
     "pkv_exchange_import", "pkv_exchange_attach", "pkv_exchange_status", "pkv_exchange_epoch",
     "pkv_home_publish_q", "pkv_home_step", "pkv_peer_step", "pkv_home_partial", "pkv_home_merge",
@@ -68,6 +68,7 @@ def lib():
         "pkv_shard_status": [vp, vp, P(u32)],
         "pkv_decode_partial": [vp, P(DecodeArgs), vp, vp, vp],
         "pkv_decode": [vp, P(DecodeArgs), vp, i32, vp, vp],
+        "pkv_decode_static": [C.c_int, P(DecodeArgs), vp, i32, vp, vp],
         "pkv_decode_splits_only": [vp, P(DecodeArgs), vp],
         "pkv_merge_partials": [C.c_int, vp, i64, vp, i64, i32, i32, i32, vp, i32, vp, vp],
         "pkv_quantize_kv": [C.c_int, vp, i32, i64, vp, vp, i32, vp],

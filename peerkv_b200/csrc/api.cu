@@ -96,6 +96,7 @@ struct pkv_shard {
   std::vector<MapEntry> maps;
   uint64_t stamp = 0;
   bool attr_set = false;
+  bool cache_maps = true;
 };
 
 struct pkv_exchange {
@@ -128,14 +129,15 @@ uint64_t* flag_ptr(pkv_exchange* x, int owner_rank, int idx) {   // idx world = 
 
 namespace {
 
-int build_map(pkv_shard* s, const void* base, const pkv_kv_view& kv, const CUtensorMap** out) {
+int build_map(pkv_shard* s, const void* base, const pkv_kv_view& kv, CUtensorMap* out) {
   MapKey key;
   memset(&key, 0, sizeof key);
   key.base = base; key.dtype = kv.dtype; key.n_kv_heads = kv.n_kv_heads;
   key.page_size = kv.page_size; key.n_pages = kv.n_pages; key.page_stride = kv.page_stride;
   key.token_stride = kv.token_stride; key.head_stride = kv.head_stride;
-  for (auto& e : s->maps)
-    if (e.key == key) { e.stamp = ++s->stamp; *out = &e.map; return PKV_OK; }
+  if (s->cache_maps)
+    for (auto& e : s->maps)
+      if (e.key == key) { e.stamp = ++s->stamp; *out = e.map; return PKV_OK; }
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return fail(PKV_E_CUDA, "cuTensorMapEncodeTiled entry point not available");
   const uint64_t es = is_16bit(kv.dtype) ? 2 : 1;
@@ -172,16 +174,16 @@ int build_map(pkv_shard* s, const void* base, const pkv_kv_view& kv, const CUten
                 "strides (page %lld, tok %lld, head %lld)",
                 (int)r, base, kv.n_kv_heads, kv.page_size, (long long)kv.n_pages,
                 (long long)kv.page_stride, (long long)kv.token_stride, (long long)kv.head_stride);
+  *out = e.map;
+  if (!s->cache_maps) return PKV_OK;   // encoding is host arithmetic only; nothing is stored
   e.stamp = ++s->stamp;
   if (s->maps.size() < 32) {
     s->maps.push_back(e);
-    *out = &s->maps.back().map;
   } else {
     size_t victim = 0;
     for (size_t i = 1; i < s->maps.size(); ++i)
       if (s->maps[i].stamp < s->maps[victim].stamp) victim = i;
     s->maps[victim] = e;
-    *out = &s->maps[victim].map;
   }
   return PKV_OK;
 }
@@ -309,13 +311,11 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   }
 
   if (kv.n_pages > 0) {
-    const CUtensorMap *mk = nullptr, *mv = nullptr;
-    rc = build_map(s, kv.k, kv, &mk);
+    CUtensorMap tk, tv;
+    rc = build_map(s, kv.k, kv, &tk);
     if (rc) return rc;
-    CUtensorMap tk = *mk;   // copy: the cache may reallocate on the second insert
-    rc = build_map(s, kv.v, kv, &mv);
+    rc = build_map(s, kv.v, kv, &tv);
     if (rc) return rc;
-    CUtensorMap tv = *mv;
     dim3 grid(n_cta_x, n_hb), block(pkv::kThreads);
     if (kv.dtype == PKV_BF16)
       pkv::decode_partial_kernel<true, kStages><<<grid, block, L::kTotal, st>>>(tk, tv, p);
@@ -762,3 +762,98 @@ int pkv_home_merge(pkv_exchange* x, int32_t batch, uint32_t wait_mask, void* out
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------- //
+// pkv_decode_static: the same decode with its scratch in static device memory
+// ------------------------------------------------------------------------- //
+namespace {
+
+constexpr int kStaticMaxBatch = 32;
+constexpr int kStaticMaxQHeads = 64;
+constexpr int kStaticMaxSms = 192;
+constexpr int kStaticMaxDevices = 16;
+constexpr size_t kStaticSlots = kStaticMaxSms + kStaticMaxBatch;
+constexpr size_t kStaticWords = 128 + (size_t)kStaticMaxBatch * kStaticMaxQHeads;
+
+// One copy per GPU that loads the library, held until the process exits (7.4 MB).
+// In host code these names are only handles for cudaGetSymbolAddress, never pointers.
+static __device__ __align__(256) float g_static_part_o[kStaticSlots * kStaticMaxQHeads * pkv::kHeadDim];
+static __device__ __align__(256) float g_static_part_ml[kStaticSlots * kStaticMaxQHeads * 2];
+static __device__ __align__(256) unsigned int g_static_words[kStaticWords];
+
+pkv_shard g_static_shard[kStaticMaxDevices];
+bool g_static_ready[kStaticMaxDevices];
+std::mutex g_static_mutex;
+
+// First call on a device: resolve the device addresses of the static arrays with that
+// device current, and raise the kernels' shared-memory limit.
+int static_setup(int device) {
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_ready[device]) return PKV_OK;
+  int sms = 0, major = 0;
+  PKV_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  PKV_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+  if (major != 10)
+    return fail(PKV_E_UNSUPPORTED, "device %d has compute capability %d.x; sm_100a only", device, major);
+  if (sms > kStaticMaxSms)
+    return fail(PKV_E_UNSUPPORTED, "device %d has %d SMs; the static scratch is sized for %d", device,
+                sms, kStaticMaxSms);
+  float *po = nullptr, *pml = nullptr;
+  unsigned int* pw = nullptr;
+  PKV_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&po), g_static_part_o));
+  PKV_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&pml), g_static_part_ml));
+  PKV_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&pw), g_static_words));
+  pkv_shard& s = g_static_shard[device];
+  s.device = device;
+  s.num_sms = sms;
+  s.max_batch = kStaticMaxBatch;
+  s.n_q_heads = 0;                       // set per call
+  s.n_slots = static_cast<int>(kStaticSlots);
+  s.part_o = po;
+  s.part_ml = pml;
+  s.status = reinterpret_cast<uint32_t*>(pw);          // words [0, 64): status block
+  s.done_counter = pw + 16;
+  s.counters = pw + 64;                                // 64 global words, then per (sequence, kv-head)
+  s.n_counter_words = kStaticWords - 64;
+  s.cache_maps = false;                                // tensor maps are encoded on the stack
+  using L = pkv::SmemLayout<kStages>;
+  PKV_CUDA(cudaFuncSetAttribute(pkv::decode_partial_kernel<true, kStages>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+  PKV_CUDA(cudaFuncSetAttribute(pkv::decode_partial_kernel<false, kStages>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+  s.attr_set = true;
+  g_static_ready[device] = true;
+  return PKV_OK;
+}
+
+}  // namespace
+
+extern "C" int pkv_decode_static(int device, const pkv_decode_args* a, void* out, int32_t out_dtype,
+                                 float* lse_out, void* stream) {
+  if (!a || !out) return fail(PKV_E_INVALID, "null args or out");
+  if (device < 0 || device >= kStaticMaxDevices) return fail(PKV_E_INVALID, "device %d", device);
+  if (out_dtype != PKV_F16 && out_dtype != PKV_BF16 && out_dtype != PKV_F32)
+    return fail(PKV_E_INVALID, "out_dtype %d", out_dtype);
+  if (a->batch < 0 || a->batch > kStaticMaxBatch)
+    return fail(PKV_E_INVALID, "batch %d exceeds the static scratch (at most %d sequences per call); "
+                "use pkv_decode with a pkv_shard for larger batches", a->batch, kStaticMaxBatch);
+  if (a->n_q_heads <= 0 || a->n_q_heads > kStaticMaxQHeads)
+    return fail(PKV_E_INVALID, "n_q_heads %d exceeds the static scratch (at most %d query heads); "
+                "use pkv_decode with a pkv_shard", a->n_q_heads, kStaticMaxQHeads);
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", device);
+  int rc = static_setup(device);
+  if (rc) return rc;
+  pkv_shard& s = g_static_shard[device];
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The arrays keep whatever the previous call left: status and arrival counters must
+  // start at zero (a call that gave up on a wait may have left them half-counted).
+  PKV_CUDA(cudaMemsetAsync(s.status, 0, kStaticWords * sizeof(unsigned int), st));
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  s.n_q_heads = a->n_q_heads;
+  LaunchOut lo;
+  lo.out = out;
+  lo.out_dtype = out_dtype;
+  lo.lse_part = lse_out;
+  return launch_decode(&s, a, lo, st);
+}
