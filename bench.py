@@ -35,8 +35,8 @@ CTX = 131072
 BYTES_PER_TOKEN = 2 * HKV * D * 2            # K and V, bf16
 PEAK_FALLBACK_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of decode_partial_kernel per launch,
-# measured with ncu on a 1 GiB pool and scaled by tokens (profiles/decode_partial_c2.md)
-NCU_TRAFFIC_PER_ALGO_BYTE = None
+# measured with ncu on a 1 GiB pool and scaled by tokens (profiles/decode_partial_bf16_paged.md)
+NCU_TRAFFIC_PER_ALGO_BYTE = (1.07455e9 + 4.46e6) / 1073741824
 
 
 def measured_peak():
