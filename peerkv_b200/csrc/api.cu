@@ -210,7 +210,15 @@ int check_args(const pkv_shard* s, const pkv_decode_args* a) {
       return fail(PKV_E_INVALID, "16-bit KV (%d) and q (%d) must share a dtype", kv.dtype,
                   a->q_dtype);
   } else if (is_quant(kv.dtype)) {
-    return fail(PKV_E_UNSUPPORTED, "quantised KV attention is not built into this library yet");
+    if (kv.n_pages > 0 && (!kv.k_scale || !kv.v_scale))
+      return fail(PKV_E_INVALID, "quantised KV needs k_scale and v_scale");
+    if (kv.page_size % pkv::kTileTok)
+      return fail(PKV_E_UNSUPPORTED, "quantised KV: page_size %d must be a multiple of 16", kv.page_size);
+    if (kv.n_kv_heads > pkv::kHeadsPerCta && kv.n_kv_heads % pkv::kHeadsPerCta)
+      return fail(PKV_E_UNSUPPORTED, "quantised KV: n_kv_heads %d must be <= 8 or a multiple of 8",
+                  kv.n_kv_heads);
+    if ((reinterpret_cast<uintptr_t>(kv.k_scale) | reinterpret_cast<uintptr_t>(kv.v_scale)) & 15)
+      return fail(PKV_E_INVALID, "scale arrays must be 16-byte aligned");
   } else {
     return fail(PKV_E_INVALID, "kv dtype %d unknown", kv.dtype);
   }
@@ -243,7 +251,26 @@ struct LaunchOut {
   uint32_t wait_mask = 0;
 };
 
-constexpr int kStages = 3;
+constexpr int kStages = 3;    // 16-bit pools: 3 K slots + 3 V slots of 32 KiB
+constexpr int kStagesQ = 6;   // 1-byte pools: 6 + 6 slots of 16 KiB
+using L16 = pkv::SmemLayout<kStages, 2>;
+using L8 = pkv::SmemLayout<kStagesQ, 1>;
+
+template <typename K>
+int set_smem(K kernel, int bytes) {
+  PKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return PKV_OK;
+}
+
+int set_kernel_attrs() {
+  int rc = set_smem(pkv::decode_partial_kernel<pkv::kKvBF16, true, kStages>, L16::kTotal);
+  if (!rc) rc = set_smem(pkv::decode_partial_kernel<pkv::kKvF16, false, kStages>, L16::kTotal);
+  if (!rc) rc = set_smem(pkv::decode_partial_kernel<pkv::kKvInt8, true, kStagesQ>, L8::kTotal);
+  if (!rc) rc = set_smem(pkv::decode_partial_kernel<pkv::kKvInt8, false, kStagesQ>, L8::kTotal);
+  if (!rc) rc = set_smem(pkv::decode_partial_kernel<pkv::kKvFp8, true, kStagesQ>, L8::kTotal);
+  if (!rc) rc = set_smem(pkv::decode_partial_kernel<pkv::kKvFp8, false, kStagesQ>, L8::kTotal);
+  return rc;
+}
 constexpr uint64_t kWaitNs = 2000000000ull;  // bound of every cross-GPU device-side wait
 
 int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, cudaStream_t st) {
@@ -252,12 +279,9 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   if (a->batch == 0) return PKV_OK;
   DeviceGuard guard(s->device);
   if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", s->device);
-  using L = pkv::SmemLayout<kStages>;
   if (!s->attr_set) {
-    PKV_CUDA(cudaFuncSetAttribute(pkv::decode_partial_kernel<true, kStages>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    PKV_CUDA(cudaFuncSetAttribute(pkv::decode_partial_kernel<false, kStages>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    rc = set_kernel_attrs();
+    if (rc) return rc;
     s->attr_set = true;
   }
   const pkv_kv_view& kv = a->kv;
@@ -286,6 +310,8 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   p.q_flag = lo.q_flag;
   p.q_epoch = lo.q_epoch;
   p.q_timeout_ns = kWaitNs;
+  p.k_scale = kv.k_scale;
+  p.v_scale = kv.v_scale;
   p.fuse = lo.skip_combine ? 0 : 1;
   p.out = lo.out;
   p.out_dtype = lo.out_dtype;
@@ -317,10 +343,19 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
     rc = build_map(s, kv.v, kv, &tv);
     if (rc) return rc;
     dim3 grid(n_cta_x, n_hb), block(pkv::kThreads);
-    if (kv.dtype == PKV_BF16)
-      pkv::decode_partial_kernel<true, kStages><<<grid, block, L::kTotal, st>>>(tk, tv, p);
-    else
-      pkv::decode_partial_kernel<false, kStages><<<grid, block, L::kTotal, st>>>(tk, tv, p);
+    const bool qbf = a->q_dtype == PKV_BF16;
+    switch (kv.dtype) {
+      case PKV_BF16: pkv::decode_partial_kernel<pkv::kKvBF16, true, kStages><<<grid, block, L16::kTotal, st>>>(tk, tv, p); break;
+      case PKV_F16: pkv::decode_partial_kernel<pkv::kKvF16, false, kStages><<<grid, block, L16::kTotal, st>>>(tk, tv, p); break;
+      case PKV_INT8:
+        if (qbf) pkv::decode_partial_kernel<pkv::kKvInt8, true, kStagesQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
+        else     pkv::decode_partial_kernel<pkv::kKvInt8, false, kStagesQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
+        break;
+      default:
+        if (qbf) pkv::decode_partial_kernel<pkv::kKvFp8, true, kStagesQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
+        else     pkv::decode_partial_kernel<pkv::kKvFp8, false, kStagesQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
+        break;
+    }
     PKV_CUDA(cudaGetLastError());
     return PKV_OK;   // the combine is fused into the kernel's tail
   }
@@ -816,11 +851,7 @@ int static_setup(int device) {
   s.counters = pw + 64;                                // 64 global words, then per (sequence, kv-head)
   s.n_counter_words = kStaticWords - 64;
   s.cache_maps = false;                                // tensor maps are encoded on the stack
-  using L = pkv::SmemLayout<kStages>;
-  PKV_CUDA(cudaFuncSetAttribute(pkv::decode_partial_kernel<true, kStages>,
-                                cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-  PKV_CUDA(cudaFuncSetAttribute(pkv::decode_partial_kernel<false, kStages>,
-                                cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+  { int rc = set_kernel_attrs(); if (rc) return rc; }
   s.attr_set = true;
   g_static_ready[device] = true;
   return PKV_OK;

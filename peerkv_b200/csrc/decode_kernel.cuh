@@ -292,24 +292,76 @@ __device__ __forceinline__ void count_done(const DecodeParams& p, unsigned int n
   }
 }
 
-template <int NSTAGE>
+// KV element kinds (the PKV_* dtype codes of the C ABI)
+constexpr int kKvF16 = 0, kKvBF16 = 1, kKvInt8 = 2, kKvFp8 = 3;
+
+template <int NSTAGE, int ES>   // ES = bytes per KV element (2, or 1 for quantised codes)
 struct SmemLayout {
-  static constexpr int kSlotBytes = kHeadsPerCta * kTileTok * kHeadDim * 2;  // 32 KiB: one K or V tile
-  static constexpr int kVOff = NSTAGE * kSlotBytes;                          // V ring after the K ring
+  static constexpr int kHeadBytes = kTileTok * kHeadDim * ES;        // one head of a tile: 4 KiB / 2 KiB
+  static constexpr int kSlotBytes = kHeadsPerCta * kHeadBytes;        // one K or V tile: 32 / 16 KiB
+  static constexpr int kVOff = NSTAGE * kSlotBytes;                   // V ring after the K ring
   static constexpr int kDataBytes = 2 * NSTAGE * kSlotBytes;
-  // barriers: full[ring][slot][head] then empty[ring][slot]
-  static constexpr int kBarOff = kDataBytes;
-  static constexpr int kNumBars = 2 * NSTAGE * kHeadsPerCta + 2 * NSTAGE;
+  // quantised pools: fp16 scales of a tile, [16 tok][8 heads], per ring and slot
+  static constexpr int kScaleSlot = kTileTok * kHeadsPerCta * 2;      // 256 B
+  static constexpr int kScaleOff = kDataBytes;
+  static constexpr int kScaleBytes = ES == 1 ? 2 * NSTAGE * kScaleSlot : 0;
+  // barriers: full[ring][slot][head], empty[ring][slot], scale_full[ring][slot]
+  static constexpr int kBarOff = kScaleOff + kScaleBytes;
+  static constexpr int kNumBars = 2 * NSTAGE * kHeadsPerCta + 4 * NSTAGE;
   static constexpr int kAbortOff = kBarOff + kNumBars * 8;
   static constexpr int kPrefixOff = kAbortOff + 16;
   static constexpr int kTotal = kPrefixOff + (kMaxBatch + 1) * 4 + 1024;  // +1024: manual alignment
 };
 
-template <bool BF16, int NSTAGE>
+// 1-byte codes -> fp16 pairs, exactly.  int8: bias the byte to unsigned, plant it in the
+// mantissa of 1024.0 (0x6400 | u = 1024 + u) and subtract 1152; e4m3: the hardware cvt.
+// `SEL_A` / `SEL_B` pick which two bytes of `r` form each pair (prmt selectors).
+template <bool FP8>
+__device__ __forceinline__ void codes_to_half2(uint32_t r, uint32_t sel_a, uint32_t sel_b,
+                                               uint32_t& a, uint32_t& b) {
+  if constexpr (FP8) {
+    // selectors here choose two source bytes into the low 16 bits (upper bytes zero)
+    uint32_t pa, pb;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(pa) : "r"(r), "r"(0u), "r"(sel_a));
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(pb) : "r"(r), "r"(0u), "r"(sel_b));
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(a) : "h"(static_cast<unsigned short>(pa)));
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(b) : "h"(static_cast<unsigned short>(pb)));
+  } else {
+    const uint32_t x = r ^ 0x80808080u;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(a) : "r"(x), "r"(0x64646464u), "r"(sel_a));
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(b) : "r"(x), "r"(0x64646464u), "r"(sel_b));
+    const uint32_t bias = 0x64806480u;   // 1152.0 twice
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(a) : "r"(a), "r"(bias));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(b) : "r"(b), "r"(bias));
+  }
+}
+
+// prmt selectors for codes_to_half2.  K (row-wise bytes): pairs (b0,b1) and (b2,b3).
+// V (after the transposed load): pairs (b0,b2) and (b1,b3).  int8 pairs are planted as
+// [0x64:hi][0x64:lo]; e4m3 pairs are packed into the low 16 bits for the hardware cvt.
+template <bool FP8> __device__ __forceinline__ constexpr uint32_t kQuantSelK0() { return FP8 ? 0x4410u : 0x4140u; }
+template <bool FP8> __device__ __forceinline__ constexpr uint32_t kQuantSelK1() { return FP8 ? 0x4432u : 0x4342u; }
+template <bool FP8> __device__ __forceinline__ constexpr uint32_t kQuantSelV0() { return FP8 ? 0x4420u : 0x4240u; }
+template <bool FP8> __device__ __forceinline__ constexpr uint32_t kQuantSelV1() { return FP8 ? 0x4431u : 0x4341u; }
+
+// two bf16 (packed) -> two fp16 (packed), round to nearest
+__device__ __forceinline__ uint32_t bf16x2_to_half2(uint32_t v) {
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&v);
+  const __half2 h = __floats2half2_rn(__low2float(b), __high2float(b));
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// KVT: kKvF16 / kKvBF16 (16-bit pools; q has the same type) or kKvInt8 / kKvFp8 (1-byte
+// codes with one fp16 scale per (token, kv-head); q is fp16 or bf16 per QBF16 and the
+// MMAs run in fp16, into which both code formats convert exactly).
+template <int KVT, bool QBF16, int NSTAGE>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const DecodeParams p) {
-  using L = SmemLayout<NSTAGE>;
+  constexpr bool kQuant = KVT >= kKvInt8;
+  constexpr bool BF16 = KVT == kKvBF16;        // operand type of the MMAs
+  constexpr int ES = kQuant ? 1 : 2;
+  using L = SmemLayout<NSTAGE, ES>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
@@ -323,6 +375,12 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
   auto empty = [&](int ring, int s) {
     return bar0 + 8u * (2 * NSTAGE * kHeadsPerCta + ring * NSTAGE + s);
   };
+  auto scale_full = [&](int ring, int s) {
+    return bar0 + 8u * (2 * NSTAGE * kHeadsPerCta + 2 * NSTAGE + ring * NSTAGE + s);
+  };
+  auto scale_smem = [&](int ring, int s) {
+    return sbase + L::kScaleOff + (ring * NSTAGE + s) * L::kScaleSlot;
+  };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hb = blockIdx.y;                   // block of 8 kv-heads
@@ -334,6 +392,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       for (int s = 0; s < NSTAGE; ++s) {
         for (int h = 0; h < kHeadsPerCta; ++h) mbar_init(full(ring, s, h), 1);
         mbar_init(empty(ring, s), heads_here);   // one arrival per consumer warp with a head
+        mbar_init(scale_full(ring, s), 1);
       }
     *abort_flag = 0;
     fence_barrier_init();
@@ -380,11 +439,20 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
     const int ring = warp - kConsumerWarps;
     const CUtensorMap* map = ring ? &tm_v : &tm_k;
     if (lane == 0) prefetch_tensormap(map);
-    const int hh = (lane >> 1) & 7;
-    const int dh = lane & 1;
-    const bool lane_active = lane < 16 && hh < heads_here;
+    // 16-bit pools: lane -> (head, half of D), 16 lanes, a [64 d][16 tok] box each.
+    // 1-byte pools: lane -> head, 8 lanes, a [128 d][16 tok] box each (also 2 KiB), and
+    // lanes 8.. copy the tile's fp16 scales.
+    const int hh = kQuant ? (lane & 7) : ((lane >> 1) & 7);
+    const int dh = kQuant ? 0 : (lane & 1);
+    const bool lane_active = lane < (kQuant ? 8 : 16) && hh < heads_here;
+    const unsigned int box_lanes = kQuant ? (0xffu >> (kHeadsPerCta - heads_here))
+                                          : (0xffffu >> (2 * (kHeadsPerCta - heads_here)));
     const uint32_t ring_base = sbase + (ring ? L::kVOff : 0);
-    const uint32_t dst_off = hh * 4096 + dh * 2048;
+    const uint32_t dst_off = hh * L::kHeadBytes + dh * 2048;
+    // scale copies: every kv-head of the pool sits in this CTA (Hkv <= 8): the tile's
+    // [16 tok][Hkv] scales are one contiguous run; otherwise one 16-byte row per token.
+    const bool scale_one = p.n_kv_heads <= kHeadsPerCta;
+    const uint8_t* scale_base = reinterpret_cast<const uint8_t*>(ring ? p.v_scale : p.k_scale);
 
     int s = find_seq(prefix, p.batch, g0);
     int it = 0;
@@ -431,11 +499,29 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
           if (!got) { ok = false; break; }
           if (lane_active) {
             const uint32_t bar = full(ring, stage, hh);
-            if (dh == 0) mbar_arrive_expect_tx(bar, 4096);
-            __syncwarp(0x0000ffffu >> (2 * (kHeadsPerCta - heads_here)));
+            if (dh == 0) mbar_arrive_expect_tx(bar, L::kHeadBytes);
+            __syncwarp(box_lanes);
             const uint32_t dst = ring_base + stage * L::kSlotBytes + dst_off;
             if (p.head_major) tma_load_4d(dst, map, bar, dh * 64, tok0, head0 + hh, page);
             else              tma_load_4d(dst, map, bar, dh * 64, head0 + hh, tok0, page);
+          }
+          if constexpr (kQuant) {
+            // scales of the tile: dense [page][tok][head] fp16
+            const int64_t row0 = ((int64_t)page * p.page_size + tok0) * p.n_kv_heads + head0;
+            const uint32_t sdst = scale_smem(ring, stage);
+            const uint32_t sbar = scale_full(ring, stage);
+            if (scale_one) {
+              if (lane == 8) {
+                const uint32_t bytes = kTileTok * p.n_kv_heads * 2;
+                mbar_arrive_expect_tx(sbar, bytes);
+                bulk_load(sdst, scale_base + row0 * 2, bytes, sbar);
+              }
+            } else if (lane >= 8 && lane < 8 + kTileTok) {
+              if (lane == 8) mbar_arrive_expect_tx(sbar, kTileTok * 16);
+              __syncwarp(0x00ffff00u);
+              const int r = lane - 8;
+              bulk_load(sdst + r * 16, scale_base + (row0 + (int64_t)r * p.n_kv_heads) * 2, 16, sbar);
+            }
           }
         }
       }
@@ -450,6 +536,12 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
           mbar_wait_bounded(full(ring, jt % NSTAGE, hh), (jt / NSTAGE) & 1, kPollLimit);
         }
       }
+      if (kQuant && lane == 8) {
+        for (int back = 1; back <= NSTAGE && back <= it; ++back) {
+          const int jt = it - back;
+          mbar_wait_bounded(scale_full(ring, jt % NSTAGE), (jt / NSTAGE) & 1, kPollLimit);
+        }
+      }
     }
     return;
   }
@@ -461,8 +553,9 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
   const int kvh = head0 + hh;
   const int g = lane >> 2, t = lane & 3;        // MMA fragment row / column-pair ids
   const int G = p.group;
-  const uint32_t koff = hh * 4096;
-  const uint32_t voff = L::kVOff + hh * 4096;
+  const uint32_t koff = hh * L::kHeadBytes;
+  const uint32_t voff = L::kVOff + hh * L::kHeadBytes;
+  const int scale_stride = p.n_kv_heads <= kHeadsPerCta ? p.n_kv_heads : kHeadsPerCta;  // halves per token row
   // ldmatrix lane addressing (row inside the [16 tok][64 d] swizzled block)
   const int krow = lane & 15, kcsel = lane >> 4;
   const int vrow = (lane & 7) + ((lane >> 4) << 3), vcsel = (lane >> 3) & 1;
@@ -500,6 +593,9 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
     }
 
     // Q^T B-fragments: column n = g is q head kvh*G + g (zero beyond the group).
+    // 16-bit pools: k-step ks covers d = 16ks..16ks+15 in the natural order.
+    // 1-byte pools: k index 2t+{0,1} of step ks is d = 16ks+4t+{0,1} and k index 2t+8+{0,1}
+    // is d = 16ks+4t+{2,3} (the order in which ldmatrix hands out code bytes).
     uint32_t qf[8][2];
     {
       const uint32_t* qrow = reinterpret_cast<const uint32_t*>(
@@ -508,8 +604,17 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       const bool have = active && g < G;
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        qf[ks][0] = have ? __ldcg(qrow + ks * 8 + t) : 0u;
-        qf[ks][1] = have ? __ldcg(qrow + ks * 8 + 4 + t) : 0u;
+        if constexpr (kQuant) {
+          qf[ks][0] = have ? __ldcg(qrow + ks * 8 + 2 * t) : 0u;
+          qf[ks][1] = have ? __ldcg(qrow + ks * 8 + 2 * t + 1) : 0u;
+          if constexpr (QBF16) {
+            qf[ks][0] = bf16x2_to_half2(qf[ks][0]);
+            qf[ks][1] = bf16x2_to_half2(qf[ks][1]);
+          }
+        } else {
+          qf[ks][0] = have ? __ldcg(qrow + ks * 8 + t) : 0u;
+          qf[ks][1] = have ? __ldcg(qrow + ks * 8 + 4 + t) : 0u;
+        }
       }
     }
     float o[8][4];
@@ -537,16 +642,45 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       float sc[4];
       if (active) {
         float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+        if constexpr (kQuant) {
+          // [16 tok][128 B] codes: one ldmatrix.x4 = two 16-byte chunks = two k-steps.
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          uint32_t a[4];
-          const uint32_t chunk = ((ks & 3) << 1) | kcsel;
-          ldmatrix_x4(a, sk + (ks >> 2) * 2048 + krow_off + ((chunk ^ kx) << 4));
-          if (ks & 1) mma_16816<BF16>(sb, a, qf[ks][0], qf[ks][1]);
-          else        mma_16816<BF16>(sa, a, qf[ks][0], qf[ks][1]);
+          for (int kp = 0; kp < 4; ++kp) {
+            uint32_t r[4], a[4];
+            const uint32_t chunk = (kp << 1) | kcsel;
+            ldmatrix_x4(r, sk + krow_off + ((chunk ^ kx) << 4));
+            // r0: tok g, chunk 2kp; r1: tok g+8, chunk 2kp; r2, r3: chunk 2kp+1
+            codes_to_half2<KVT == kKvFp8>(r[0], kQuantSelK0<KVT == kKvFp8>(), kQuantSelK1<KVT == kKvFp8>(), a[0], a[2]);
+            codes_to_half2<KVT == kKvFp8>(r[1], kQuantSelK0<KVT == kKvFp8>(), kQuantSelK1<KVT == kKvFp8>(), a[1], a[3]);
+            mma_16816<false>(sa, a, qf[2 * kp][0], qf[2 * kp][1]);
+            codes_to_half2<KVT == kKvFp8>(r[2], kQuantSelK0<KVT == kKvFp8>(), kQuantSelK1<KVT == kKvFp8>(), a[0], a[2]);
+            codes_to_half2<KVT == kKvFp8>(r[3], kQuantSelK0<KVT == kKvFp8>(), kQuantSelK1<KVT == kKvFp8>(), a[1], a[3]);
+            mma_16816<false>(sb, a, qf[2 * kp + 1][0], qf[2 * kp + 1][1]);
+          }
+          // per-token K scales (rows g and g+8 of the score tile)
+          got = false;
+          for (uint32_t w = 0; w < kPollLimit; ++w) {
+            if (mbar_try_wait(scale_full(0, stage), ph)) { got = true; break; }
+            if (*abort_flag) break;
+          }
+          if (!got) { if (lane == 0) { atomicOr(p.status, kStPipeTimeout); *abort_flag = 1; } return; }
+          const __half* ksc = reinterpret_cast<const __half*>(sgen + L::kScaleOff + stage * L::kScaleSlot);
+          const float k0 = __half2float(ksc[g * scale_stride + hh]) * p.scale_log2;
+          const float k1 = __half2float(ksc[(g + 8) * scale_stride + hh]) * p.scale_log2;
+          sc[0] = (sa[0] + sb[0]) * k0; sc[1] = (sa[1] + sb[1]) * k0;
+          sc[2] = (sa[2] + sb[2]) * k1; sc[3] = (sa[3] + sb[3]) * k1;
+        } else {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            uint32_t a[4];
+            const uint32_t chunk = ((ks & 3) << 1) | kcsel;
+            ldmatrix_x4(a, sk + (ks >> 2) * 2048 + krow_off + ((chunk ^ kx) << 4));
+            if (ks & 1) mma_16816<BF16>(sb, a, qf[ks][0], qf[ks][1]);
+            else        mma_16816<BF16>(sa, a, qf[ks][0], qf[ks][1]);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) sc[i] = (sa[i] + sb[i]) * p.scale_log2;
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) sc[i] = (sa[i] + sb[i]) * p.scale_log2;
         if (valid < kTileTok) {
           if (g >= valid) { sc[0] = -INFINITY; sc[1] = -INFINITY; }
           if (g + 8 >= valid) { sc[2] = -INFINITY; sc[3] = -INFINITY; }
@@ -585,6 +719,21 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       if (!got) { if (lane == 0) { atomicOr(p.status, kStPipeTimeout); *abort_flag = 1; } return; }
 
       if (active) {
+        if constexpr (kQuant) {
+          // fold the per-token V scales into P (tokens g and g+8; 0 past the end so that a
+          // garbage scale there cannot poison the sum)
+          bool gots = false;
+          for (uint32_t w = 0; w < kPollLimit; ++w) {
+            if (mbar_try_wait(scale_full(1, stage), ph)) { gots = true; break; }
+            if (*abort_flag) break;
+          }
+          if (!gots) { if (lane == 0) { atomicOr(p.status, kStPipeTimeout); *abort_flag = 1; } return; }
+          const __half* vsc = reinterpret_cast<const __half*>(
+              sgen + L::kScaleOff + (NSTAGE + stage) * L::kScaleSlot);
+          const float v0 = g < valid ? __half2float(vsc[g * scale_stride + hh]) : 0.f;
+          const float v1 = g + 8 < valid ? __half2float(vsc[(g + 8) * scale_stride + hh]) : 0.f;
+          sc[0] *= v0; sc[1] *= v0; sc[2] *= v1; sc[3] *= v1;
+        }
         // P^T as the B operand: transpose the two 8x8 (tok x head) blocks.
         const uint32_t b0 = movmatrix_trans(pack2<BF16>(sc[0], sc[1]));
         const uint32_t b1 = movmatrix_trans(pack2<BF16>(sc[2], sc[3]));
@@ -595,13 +744,35 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
           mk01 = (2 * t < valid ? 0x0000ffffu : 0u) | (2 * t + 1 < valid ? 0xffff0000u : 0u);
           mk23 = (2 * t + 8 < valid ? 0x0000ffffu : 0u) | (2 * t + 9 < valid ? 0xffff0000u : 0u);
         }
+        if constexpr (kQuant) {
+          // Transposed 8x8 "b16" loads over code bytes deliver, per thread, the byte pairs
+          // (d = 2g, 2g+1) of tokens 2t and 2t+1: bytes (0,2) are row d = 16c+2g of V^T and
+          // bytes (1,3) row d = 16c+2g+1.  So MMA row g is d = 16c+2g and row g+8 is
+          // d = 16c+2g+1; the flush below writes O with that mapping.
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          uint32_t a[4];
-          const uint32_t chunk = ((j & 3) << 1) | vcsel;
-          ldmatrix_x4_trans(a, sv + (j >> 2) * 2048 + vrow_off + ((chunk ^ vx) << 4));
-          a[0] &= mk01; a[1] &= mk01; a[2] &= mk23; a[3] &= mk23;
-          mma_16816<BF16>(o[j], a, b0, b1);
+          for (int jp = 0; jp < 4; ++jp) {
+            uint32_t r[4], a[4];
+            const uint32_t chunk = (jp << 1) | kcsel;
+            ldmatrix_x4_trans(r, sv + krow_off + ((chunk ^ kx) << 4));
+            // r0: toks 0-7, chunk 2jp; r1: toks 8-15, chunk 2jp; r2, r3: chunk 2jp+1
+            codes_to_half2<KVT == kKvFp8>(r[0], kQuantSelV0<KVT == kKvFp8>(), kQuantSelV1<KVT == kKvFp8>(), a[0], a[1]);
+            codes_to_half2<KVT == kKvFp8>(r[1], kQuantSelV0<KVT == kKvFp8>(), kQuantSelV1<KVT == kKvFp8>(), a[2], a[3]);
+            a[0] &= mk01; a[1] &= mk01; a[2] &= mk23; a[3] &= mk23;
+            mma_16816<false>(o[2 * jp], a, b0, b1);
+            codes_to_half2<KVT == kKvFp8>(r[2], kQuantSelV0<KVT == kKvFp8>(), kQuantSelV1<KVT == kKvFp8>(), a[0], a[1]);
+            codes_to_half2<KVT == kKvFp8>(r[3], kQuantSelV0<KVT == kKvFp8>(), kQuantSelV1<KVT == kKvFp8>(), a[2], a[3]);
+            a[0] &= mk01; a[1] &= mk01; a[2] &= mk23; a[3] &= mk23;
+            mma_16816<false>(o[2 * jp + 1], a, b0, b1);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint32_t a[4];
+            const uint32_t chunk = ((j & 3) << 1) | vcsel;
+            ldmatrix_x4_trans(a, sv + (j >> 2) * 2048 + vrow_off + ((chunk ^ vx) << 4));
+            a[0] &= mk01; a[1] &= mk01; a[2] &= mk23; a[3] &= mk23;
+            mma_16816<BF16>(o[j], a, b0, b1);
+          }
         }
       }
       __syncwarp();
@@ -620,14 +791,17 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       const int h0 = 2 * t, h1 = 2 * t + 1;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const int d = 16 * j + g;
+        // accumulator rows g and g+8 of m-tile j: d = 16j+g, 16j+g+8 (16-bit pools) or
+        // d = 16j+2g, 16j+2g+1 (1-byte pools, see the PV loop)
+        const int d = kQuant ? 16 * j + 2 * g : 16 * j + g;
+        const int d2 = kQuant ? d + 1 : d + 8;
         if (h0 < G) {
           p.part_o[(hbase + h0) * kHeadDim + d] = o[j][0];
-          p.part_o[(hbase + h0) * kHeadDim + d + 8] = o[j][2];
+          p.part_o[(hbase + h0) * kHeadDim + d2] = o[j][2];
         }
         if (h1 < G) {
           p.part_o[(hbase + h1) * kHeadDim + d] = o[j][1];
-          p.part_o[(hbase + h1) * kHeadDim + d + 8] = o[j][3];
+          p.part_o[(hbase + h1) * kHeadDim + d2] = o[j][3];
         }
       }
       if (g == 0) {
