@@ -176,6 +176,116 @@ def workload_config(n):
 
 
 # --------------------------------------------------------------------------- #
+# workloads (synthetic stand-ins with the shapes, sizes and value distributions of the
+# BASELINE configurations; N(0,1) KV, seeded)
+# --------------------------------------------------------------------------- #
+WORKLOADS = {
+    # name: batch, Hq, Hkv, tokens per sequence (None = ragged), kv format, placement
+    "paged-bf16": dict(B=16, HQ=32, HKV=8, ctx=131072, fmt="bf16", place="round_robin"),
+    "ragged-bf16": dict(B=64, HQ=32, HKV=8, ctx=None, fmt="bf16", place="capacity_spill"),
+    "quant-int8": dict(B=8, HQ=64, HKV=8, ctx=524288, fmt="int8", place="round_robin"),
+    "quant-fp8": dict(B=8, HQ=64, HKV=8, ctx=524288, fmt="fp8", place="round_robin"),
+    "long-bf16": dict(B=4, HQ=32, HKV=8, ctx=1048576, fmt="bf16", place="round_robin"),
+}
+
+
+def build_workload(name, context, N, rank, dev):
+    """This rank's pool, local block table and shard lengths.  The global block table
+    is the same seeded permutation on every rank; placement decides which pages are
+    this rank's (round robin: page p -> GPU p mod N at index p div N; capacity spill:
+    GPUs are filled in order up to a seeded fraction in [0.5, 1.0] of an equal share,
+    the rest spills to the next GPU)."""
+    import numpy as np
+    import torch
+    from peerkv_b200 import _lib, ops
+    w = WORKLOADS[name]
+    B, HQ, HKV = w["B"], w["HQ"], w["HKV"]
+    rng = np.random.default_rng(1234)
+    if w["ctx"] is None:
+        lens = rng.integers(4096, 262144 + 1, size=B).astype(np.int64)
+        if context:
+            lens = np.maximum(1, lens * context // 262144)
+    else:
+        lens = np.full(B, context or w["ctx"], dtype=np.int64)
+    n_pages = (lens + PAGE - 1) // PAGE
+    total_pages = int(n_pages.sum())
+    W = int(n_pages.max())
+    perm = rng.permutation(total_pages).astype(np.int32)
+    bt = np.zeros((B, W), dtype=np.int32)
+    k = 0
+    for i in range(B):
+        bt[i, :n_pages[i]] = perm[k:k + n_pages[i]]
+        k += int(n_pages[i])
+    sl = lens.astype(np.int32)
+
+    if w["place"] == "round_robin":
+        btd, sld = torch.from_numpy(bt).to(dev), torch.from_numpy(sl).to(dev)
+        tabs = [torch.zeros(B, W, dtype=torch.int32, device=dev) for _ in range(N)]
+        lns = [torch.zeros(B, dtype=torch.int32, device=dev) for _ in range(N)]
+        _lib.check(_lib.lib().pkv_split_block_table(
+            dev.index, btd.data_ptr(), W, sld.data_ptr(), B, PAGE, N, 1, None,
+            (C.c_void_p * N)(*[t.data_ptr() for t in tabs]), W,
+            (C.c_void_p * N)(*[t.data_ptr() for t in lns]), ops._stream(dev)))
+        torch.cuda.synchronize()
+        my_tab, my_len = tabs[rank], lns[rank]
+        n_local = (total_pages + N - 1) // N
+        rank_tokens = [int(x.sum()) for x in lns]
+    else:
+        caps = np.random.default_rng(99).uniform(0.5, 1.0, size=N)
+        quota = [int(c * total_pages / N) for c in caps]
+        quota[-1] = total_pages
+        tab = np.zeros((N, B, W), dtype=np.int32)
+        cnt = np.zeros((N, B), dtype=np.int64)
+        tok = np.zeros((N, B), dtype=np.int64)
+        used = np.zeros(N, dtype=np.int64)
+        g = 0
+        for i in range(B):
+            for j in range(int(n_pages[i])):
+                while g < N - 1 and used[g] >= quota[g]:
+                    g += 1
+                tab[g, i, cnt[g, i]] = used[g]                # pools are compact: local id = arrival order
+                cnt[g, i] += 1
+                used[g] += 1
+                tok[g, i] += PAGE if j < n_pages[i] - 1 else lens[i] - (n_pages[i] - 1) * PAGE
+        my_tab = torch.from_numpy(tab[rank]).to(dev)
+        my_len = torch.from_numpy(tok[rank].astype(np.int32)).to(dev)
+        n_local = max(1, int(used[rank]))
+        rank_tokens = [int(tok[r].sum()) for r in range(N)]
+
+    torch.manual_seed(100 + rank)
+    fmt = w["fmt"]
+    scales = None
+    if fmt == "bf16":
+        pool = torch.empty(2, n_local, PAGE, HKV, D, dtype=torch.bfloat16, device=dev)
+        chunk = max(1, n_local // 8)
+        for i in range(0, n_local, chunk):
+            pool[:, i:i + chunk].normal_()
+        bpt = 2 * HKV * D * 2
+    else:
+        code_dt = torch.int8 if fmt == "int8" else torch.float8_e4m3fn
+        pool = torch.empty(2, n_local, PAGE, HKV, D, dtype=code_dt, device=dev)
+        sc = torch.empty(2, n_local, PAGE, HKV, dtype=torch.float16, device=dev)
+        chunk = max(1, n_local // 32)
+        for i in range(0, n_local, chunk):                    # quantise N(0,1) bf16 with the library's quantiser
+            x = torch.randn(2, min(chunk, n_local - i), PAGE, HKV, D, device=dev).bfloat16()
+            c, s_ = ops.quantize_kv(x, fmt)
+            pool[:, i:i + chunk] = c
+            sc[:, i:i + chunk] = s_
+        scales = (sc[0], sc[1])
+        bpt = 2 * HKV * D + 2 * HKV * 2
+    ctx_desc = "ragged U[4096, 262144]" if w["ctx"] is None else str(int(lens[0]))
+    cfg = {"workload": f"{name}: batch {B}, Hq {HQ}, Hkv {HKV}, head_dim {D}, context {ctx_desc}/seq, "
+                       f"{fmt} KV, {PAGE}-token pages, random-permutation block table",
+           "batch": B, "context": ctx_desc, "page_size": PAGE,
+           "sharding": f"{w['place']} pages over {N} GPU(s), q and merge on GPU 0",
+           "l2_policy": "inputs larger than L2 (KV per GPU >= 1 GiB, read once per step)"}
+    return dict(B=B, HQ=HQ, HKV=HKV, pool=pool, scales=scales, tab=my_tab, len=my_len,
+                bytes_per_token=bpt, total_tokens=int(lens.sum()), max_rank_tokens=max(rank_tokens),
+                q_dtype=torch.bfloat16, dtype="bf16" if fmt == "bf16" else "f16",
+                config=cfg)
+
+
+# --------------------------------------------------------------------------- #
 # our arm
 # --------------------------------------------------------------------------- #
 def main():
@@ -184,7 +294,11 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--context", type=int, default=CTX, help="tokens per sequence (parity/ncu runs use less)")
+    ap.add_argument("--workload", default="paged-bf16",
+                    choices=["paged-bf16", "ragged-bf16", "quant-int8", "quant-fp8", "long-bf16"],
+                    help="paged-bf16 is the headline configuration; the others are the remaining "
+                         "BASELINE configurations' attention shapes")
+    ap.add_argument("--context", type=int, default=0, help="tokens per sequence, 0 = the workload's own")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--lean", action="store_true", help="timed steps only (for runs under a profiler)")
     args = ap.parse_args()
@@ -206,44 +320,23 @@ def main():
     if N > 1:
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
-    ctx = args.context
-    assert ctx % PAGE == 0
-    pages_per_seq = ctx // PAGE
-    total_pages = B * pages_per_seq
-    assert total_pages % N == 0
-    n_local = total_pages // N
-
-    # global block table: the same seeded permutation on every rank
-    g = torch.Generator().manual_seed(1234)
-    bt_global = torch.randperm(total_pages, generator=g).to(torch.int32).view(B, pages_per_seq)
-    sl_global = torch.full((B,), ctx, dtype=torch.int32)
-    # this rank's pool (pages p with p mod N == rank), N(0,1) bf16
-    torch.manual_seed(100 + rank)
-    pool = torch.empty(2, n_local, PAGE, HKV, D, dtype=torch.bfloat16, device=dev)
-    chunk = max(1, n_local // 8)
-    for i in range(0, n_local, chunk):
-        pool[:, i:i + chunk].normal_()
-    # placement on the device: split the global table into this rank's local table
-    btd, sld = bt_global.to(dev), sl_global.to(dev)
-    tabs = [torch.zeros(B, pages_per_seq, dtype=torch.int32, device=dev) for _ in range(N)]
-    lens = [torch.zeros(B, dtype=torch.int32, device=dev) for _ in range(N)]
-    _lib.check(_lib.lib().pkv_split_block_table(
-        dev.index, btd.data_ptr(), pages_per_seq, sld.data_ptr(), B, PAGE, N, 1, None,
-        (C.c_void_p * N)(*[t.data_ptr() for t in tabs]), pages_per_seq,
-        (C.c_void_p * N)(*[t.data_ptr() for t in lens]), ops._stream(dev)))
-    torch.cuda.synchronize()
-    my_tab, my_len = tabs[rank], lens[rank]
+    wl = build_workload(args.workload, args.context, N, rank, dev)
+    B, HQ, HKV = wl["B"], wl["HQ"], wl["HKV"]
+    pool, my_tab, my_len = wl["pool"], wl["tab"], wl["len"]
     local_tokens = int(my_len.sum())
+    bytes_per_token = wl["bytes_per_token"]
+    qdt = wl["q_dtype"]
 
     torch.manual_seed(7)
-    q_host = torch.randn(B, HQ, D).bfloat16().pin_memory()
+    q_host = torch.randn(B, HQ, D).to(qdt).pin_memory()
     q = q_host.to(dev)
-    out = torch.empty(B, HQ, D, dtype=torch.bfloat16, device=dev)
-    out_host = torch.empty(B, HQ, D, dtype=torch.bfloat16).pin_memory()
+    out = torch.empty(B, HQ, D, dtype=qdt, device=dev)
+    out_host = torch.empty(B, HQ, D, dtype=qdt).pin_memory()
     tab_host = my_tab.cpu().pin_memory()
     len_host = my_len.cpu().pin_memory()
     scale = 1.0 / math.sqrt(D)
-    view = ops.paged_view(pool[0], pool[1])
+    view = ops.paged_view(pool[0], pool[1], *(wl["scales"] or (None, None)))
+    out_code = ops._DT[qdt]
     L = _lib.lib()
     st = ops._stream(dev)
 
@@ -252,7 +345,7 @@ def main():
         a = ops.make_args(q, view, my_tab, my_tab.stride(0), my_len, scale)
 
         def step():
-            _lib.check(L.pkv_decode(shard._h, C.byref(a), out.data_ptr(), _lib.PKV_BF16, None, st))
+            _lib.check(L.pkv_decode(shard._h, C.byref(a), out.data_ptr(), out_code, None, st))
         launches_per_step = 1
         grp = None
     else:
@@ -302,7 +395,7 @@ def main():
     clocks = sampler.stop() if sampler else None
     status = shard.status() | (grp.xchg.status() if grp else 0)
 
-    algo_bytes = B * ctx * BYTES_PER_TOKEN
+    algo_bytes = wl["total_tokens"] * bytes_per_token
     value = algo_bytes / (ms_per_step * 1e-3) / 1e9
 
     # ---- end to end: host buffers in, host result out, every step ------------- #
@@ -339,15 +432,15 @@ def main():
 
     if rank == 0:
         peak, peak_kind = measured_peak()
-        kern_bytes = local_tokens * BYTES_PER_TOKEN
+        kern_bytes = local_tokens * bytes_per_token
         achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
         line = {
             "metric": "decode_attn_effective_kv_bandwidth", "value": value, "unit": "GB/s",
             "n_gpus": N, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
             "us_per_layer": ms_per_step * 1e3, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": workload_config(N) if ctx == CTX else dict(workload_config(N), context=ctx,
-                                                                 kv_bytes_per_layer=algo_bytes),
+            "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
+            "config": dict(wl["config"], kv_bytes_per_layer=algo_bytes,
+                           max_rank_kv_bytes=wl["max_rank_tokens"] * bytes_per_token),
             "frac_of_aggregate_hbm": value / (peak * N), "frac_of_8tbs_nominal": value / (8000.0 * N),
             "roofline": {"kernel": "decode_partial_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
@@ -362,7 +455,7 @@ def main():
             "clocks": dict(clocks or {}, note=f"sampled over the timed steps plus {soak_steps} more identical steps"),
             "device_status": status,
         }
-        if N == 1 and not args.no_cpu_baseline and not args.lean:
+        if N == 1 and not args.no_cpu_baseline and not args.lean and args.workload == "paged-bf16":
             cores = os.cpu_count() or 1
             torch.set_num_threads(cores)
             tokens = 131072

@@ -253,6 +253,7 @@ struct LaunchOut {
 
 constexpr int kStages = 3;    // 16-bit pools: 3 K slots + 3 V slots of 32 KiB
 constexpr int kStagesQ = 6;   // 1-byte pools: 6 + 6 slots of 16 KiB
+constexpr int kWphQ = 2;      // 1-byte pools: two consumer warps per kv-head, alternate tiles
 using L16 = pkv::SmemLayout<kStages, 2>;
 using L8 = pkv::SmemLayout<kStagesQ, 1>;
 
@@ -263,12 +264,12 @@ int set_smem(K kernel, int bytes) {
 }
 
 int set_kernel_attrs() {
-  int rc = set_smem(pkv::decode_partial_kernel<pkv::kKvBF16, true, kStages>, L16::kTotal);
-  if (!rc) rc = set_smem(pkv::decode_partial_kernel<pkv::kKvF16, false, kStages>, L16::kTotal);
-  if (!rc) rc = set_smem(pkv::decode_partial_kernel<pkv::kKvInt8, true, kStagesQ>, L8::kTotal);
-  if (!rc) rc = set_smem(pkv::decode_partial_kernel<pkv::kKvInt8, false, kStagesQ>, L8::kTotal);
-  if (!rc) rc = set_smem(pkv::decode_partial_kernel<pkv::kKvFp8, true, kStagesQ>, L8::kTotal);
-  if (!rc) rc = set_smem(pkv::decode_partial_kernel<pkv::kKvFp8, false, kStagesQ>, L8::kTotal);
+  int rc = set_smem(pkv::decode_partial_kernel<pkv::kKvBF16, true, kStages, 1>, L16::kTotal);
+  if (!rc) rc = set_smem(pkv::decode_partial_kernel<pkv::kKvF16, false, kStages, 1>, L16::kTotal);
+  if (!rc) rc = set_smem(pkv::decode_partial_kernel<pkv::kKvInt8, true, kStagesQ, kWphQ>, L8::kTotal);
+  if (!rc) rc = set_smem(pkv::decode_partial_kernel<pkv::kKvInt8, false, kStagesQ, kWphQ>, L8::kTotal);
+  if (!rc) rc = set_smem(pkv::decode_partial_kernel<pkv::kKvFp8, true, kStagesQ, kWphQ>, L8::kTotal);
+  if (!rc) rc = set_smem(pkv::decode_partial_kernel<pkv::kKvFp8, false, kStagesQ, kWphQ>, L8::kTotal);
   return rc;
 }
 constexpr uint64_t kWaitNs = 2000000000ull;  // bound of every cross-GPU device-side wait
@@ -342,18 +343,19 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
     if (rc) return rc;
     rc = build_map(s, kv.v, kv, &tv);
     if (rc) return rc;
-    dim3 grid(n_cta_x, n_hb), block(pkv::kThreads);
+    dim3 grid(n_cta_x, n_hb);
+    const dim3 block(pkv::cta_threads(is_quant(kv.dtype) ? kWphQ : 1));
     const bool qbf = a->q_dtype == PKV_BF16;
     switch (kv.dtype) {
-      case PKV_BF16: pkv::decode_partial_kernel<pkv::kKvBF16, true, kStages><<<grid, block, L16::kTotal, st>>>(tk, tv, p); break;
-      case PKV_F16: pkv::decode_partial_kernel<pkv::kKvF16, false, kStages><<<grid, block, L16::kTotal, st>>>(tk, tv, p); break;
+      case PKV_BF16: pkv::decode_partial_kernel<pkv::kKvBF16, true, kStages, 1><<<grid, block, L16::kTotal, st>>>(tk, tv, p); break;
+      case PKV_F16: pkv::decode_partial_kernel<pkv::kKvF16, false, kStages, 1><<<grid, block, L16::kTotal, st>>>(tk, tv, p); break;
       case PKV_INT8:
-        if (qbf) pkv::decode_partial_kernel<pkv::kKvInt8, true, kStagesQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
-        else     pkv::decode_partial_kernel<pkv::kKvInt8, false, kStagesQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
+        if (qbf) pkv::decode_partial_kernel<pkv::kKvInt8, true, kStagesQ, kWphQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
+        else     pkv::decode_partial_kernel<pkv::kKvInt8, false, kStagesQ, kWphQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
         break;
       default:
-        if (qbf) pkv::decode_partial_kernel<pkv::kKvFp8, true, kStagesQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
-        else     pkv::decode_partial_kernel<pkv::kKvFp8, false, kStagesQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
+        if (qbf) pkv::decode_partial_kernel<pkv::kKvFp8, true, kStagesQ, kWphQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
+        else     pkv::decode_partial_kernel<pkv::kKvFp8, false, kStagesQ, kWphQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
         break;
     }
     PKV_CUDA(cudaGetLastError());
@@ -425,7 +427,7 @@ int pkv_shard_create(pkv_shard** out, int device, int max_batch, int n_q_heads) 
   s->num_sms = sms;
   s->max_batch = max_batch;
   s->n_q_heads = n_q_heads;
-  s->n_slots = sms + max_batch;
+  s->n_slots = (sms + max_batch) * pkv::kMaxWph;
   s->maps.reserve(32);
   const size_t o_bytes = (size_t)s->n_slots * n_q_heads * pkv::kHeadDim * sizeof(float);
   const size_t ml_bytes = (size_t)s->n_slots * n_q_heads * 2 * sizeof(float);
@@ -807,10 +809,10 @@ constexpr int kStaticMaxBatch = 32;
 constexpr int kStaticMaxQHeads = 64;
 constexpr int kStaticMaxSms = 192;
 constexpr int kStaticMaxDevices = 16;
-constexpr size_t kStaticSlots = kStaticMaxSms + kStaticMaxBatch;
+constexpr size_t kStaticSlots = (size_t)(kStaticMaxSms + kStaticMaxBatch) * pkv::kMaxWph;
 constexpr size_t kStaticWords = 128 + (size_t)kStaticMaxBatch * kStaticMaxQHeads;
 
-// One copy per GPU that loads the library, held until the process exits (7.4 MB).
+// One copy per GPU that loads the library, held until the process exits (14.8 MB).
 // In host code these names are only handles for cudaGetSymbolAddress, never pointers.
 static __device__ __align__(256) float g_static_part_o[kStaticSlots * kStaticMaxQHeads * pkv::kHeadDim];
 static __device__ __align__(256) float g_static_part_ml[kStaticSlots * kStaticMaxQHeads * 2];

@@ -32,10 +32,12 @@ namespace pkv {
 constexpr int kHeadDim = 128;
 constexpr int kTileTok = 16;
 constexpr int kHeadsPerCta = 8;
-constexpr int kConsumerWarps = 8;
 constexpr int kProducerWarps = 2;   // one feeds the K ring, one the V ring
-constexpr int kServiceWarp = kConsumerWarps + kProducerWarps;  // rows of token-less sequences
-constexpr int kThreads = (kConsumerWarps + kProducerWarps + 1) * 32;
+// Consumer warps per kv-head (WPH): 1, or 2 taking alternate tiles where the per-tile
+// work is heavier than HBM leaves time for (1-byte pools).  Warp order in a CTA:
+// 8*WPH consumers, 2 producers, 1 service warp.
+constexpr int kMaxWph = 2;
+__host__ __device__ constexpr int cta_threads(int wph) { return (kHeadsPerCta * wph + kProducerWarps + 1) * 32; }
 constexpr int kMaxBatch = 4096;
 
 constexpr uint32_t kPollLimit = 1u << 20;  // polls of mbarrier.try_wait before giving up
@@ -173,7 +175,7 @@ __device__ __forceinline__ void fold_slot(float& M, float& L, float4& acc, float
   M = mn;
 }
 
-// One warp merges the per-CTA partial slots c0..c1 of sequence b for up to four query
+// One warp merges the partial slots c0..c1 (absolute slot indices) of sequence b for up to four query
 // heads qh0.. and writes their rows; each lane owns 4 of the 128 dims.  c1 < c0 means
 // the shard holds no token of the sequence.  This runs in the kernel's tail, where a
 // dependent chain of L2 round trips is what costs, so each step first issues all
@@ -195,7 +197,7 @@ __device__ __forceinline__ void combine_heads4(const DecodeParams& p, int b, int
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {
       const int c = min(base + jj, c1);           // clamped: a valid row even past the end
-      const int64_t row0 = (int64_t)(c + b) * p.n_q_heads + qh0;
+      const int64_t row0 = (int64_t)c * p.n_q_heads + qh0;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int64_t row = row0 + (i < nh ? i : 0);
@@ -354,13 +356,15 @@ __device__ __forceinline__ uint32_t bf16x2_to_half2(uint32_t v) {
 // KVT: kKvF16 / kKvBF16 (16-bit pools; q has the same type) or kKvInt8 / kKvFp8 (1-byte
 // codes with one fp16 scale per (token, kv-head); q is fp16 or bf16 per QBF16 and the
 // MMAs run in fp16, into which both code formats convert exactly).
-template <int KVT, bool QBF16, int NSTAGE>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int KVT, bool QBF16, int NSTAGE, int WPH>
+__global__ void __launch_bounds__(cta_threads(WPH), 1)
 decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const DecodeParams p) {
   constexpr bool kQuant = KVT >= kKvInt8;
   constexpr bool BF16 = KVT == kKvBF16;        // operand type of the MMAs
   constexpr int ES = kQuant ? 1 : 2;
+  constexpr int kConsumerWarps = kHeadsPerCta * WPH;
+  constexpr int kServiceWarp = kConsumerWarps + kProducerWarps;
   using L = SmemLayout<NSTAGE, ES>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -547,7 +551,8 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
   }
 
   // -------------------------------- consumers -------------------------------- //
-  const int hh = warp;                          // kv-head inside the block of 8
+  const int hh = warp & (kHeadsPerCta - 1);     // kv-head inside the block of 8
+  const int par = warp / kHeadsPerCta;          // which of the WPH alternating tile streams
   if (hh >= heads_here) return;                 // no head for this warp in a partial block
   const bool active = true;
   const int kvh = head0 + hh;
@@ -623,6 +628,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
     for (int ti = gt - prefix[s]; gt < seg_end; ++gt, ++ti, ++it) {
+      if (WPH > 1 && (it % WPH) != par) continue;   // the sibling warp's tile
       const int stage = it % NSTAGE;
       const uint32_t ph = (it / NSTAGE) & 1;
       // valid tokens of this tile
@@ -786,7 +792,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
         l0 += __shfl_xor_sync(0xffffffffu, l0, off);
         l1 += __shfl_xor_sync(0xffffffffu, l1, off);
       }
-      const int slot = blockIdx.x + s;
+      const int slot = (blockIdx.x + s) * WPH + par;
       const int64_t hbase = (int64_t)slot * p.n_q_heads + (int64_t)kvh * G;
       const int h0 = 2 * t, h1 = 2 * t + 1;
 #pragma unroll
@@ -816,20 +822,21 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       // CTA-wide meeting, so the other warps run straight into the next sequence.
       const int t0s = prefix[s], t1s = prefix[s + 1];
       const int c0 = t0s / per, c1 = (t1s - 1) / per;
+      const int slot_lo = (c0 + s) * WPH, slot_hi = (c1 + s) * WPH + WPH - 1;
       __threadfence();
       __syncwarp();
       int last = 0;
       if (lane == 0) {
         unsigned int* ctr = p.seq_counter + (size_t)s * p.n_kv_heads + kvh;
         const unsigned int prev = atomicAdd(ctr, 1u);
-        last = prev == (unsigned int)(c1 - c0);
+        last = prev == (unsigned int)(slot_hi - slot_lo);
         if (last) *ctr = 0;
         __threadfence();
       }
       last = __shfl_sync(0xffffffffu, last, 0);
       if (last && p.mg_n > 0) last = wait_peer_flags(p, lane) ? 1 : 0;   // home: peers' rows needed
       if (last) {
-        combine_group(p, s, kvh * G, G, c0, c1, lane);
+        combine_group(p, s, kvh * G, G, slot_lo, slot_hi, lane);
         if (p.done_flag) {
           __threadfence_system();
           __syncwarp();
