@@ -1,0 +1,116 @@
+"""Drop-in for `umallm.peerkv.vllm_backend` (PeerKV umallm/peerkv/vllm_backend.py:42-125):
+a vLLM attention impl that keeps the peer KV pages ON the peer GPUs and runs the
+compute-follows-KV decode there, merging on the home GPU.
+
+Same names and contract as the reference: `PeerKVFusedAttentionImpl` with
+`set_peer_kv(peer_cache, peer_base)`, `_try_fused` (returns None to fall back),
+`forward`; `register_peerkv_fused()`.  Correct-or-fallback: decode-only batches with
+head size 128 take the fused path, anything else -- prefill, chunked batches, a
+missing peer cache, any exception -- defers to the parent FlashAttention impl.
+
+Written against the vLLM that is installed here (0.22: `forward(layer, query, key,
+value, kv_cache, attn_metadata, output, output_scale=None, output_block_scale=None)`,
+KV-cache update done by the caller, metadata fields `num_actual_tokens`,
+`max_query_len`, `seq_lens`, `block_table`); the reference targets 0.8.5's 7-argument
+forward.  `peer_cache` / `peer_base` may be lists (one per extra GPU).
+"""
+from __future__ import annotations
+
+import logging
+import math
+import os
+from typing import Optional
+
+import torch
+
+from .paged import paged_cfk_decode
+
+logger = logging.getLogger("peerkv.attn")
+
+try:
+    from vllm.v1.attention.backends.flash_attn import FlashAttentionImpl
+    _HAVE_VLLM = True
+except Exception:  # noqa: BLE001 - vLLM absent or not importable on this host
+    FlashAttentionImpl = object  # type: ignore
+    _HAVE_VLLM = False
+
+
+class PeerKVFusedAttentionImpl(FlashAttentionImpl):
+    """FlashAttention impl whose decode phase runs on the GPUs that hold the KV."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self._init_peerkv()
+
+    def _init_peerkv(self):
+        self._peer_cache = None            # [2, nb_p, bs, HKV, D] on a peer GPU, or a list of them
+        self._peer_base = 1 << 30          # global block id >= this -> peer (or a list of thresholds)
+        self._splits = int(os.environ.get("PEERKV_SPLITS", 16))   # accepted for compatibility, unused
+        self._scale_override = None
+        self.fused_calls = 0
+        self.fallback_calls = 0
+
+    def set_peer_kv(self, peer_cache, peer_base) -> None:
+        """The allocator hands this layer its peer paged KV cache(s) and the global
+        block-id threshold(s) at/above which blocks live on the peer(s)."""
+        self._peer_cache = peer_cache
+        self._peer_base = list(peer_base) if isinstance(peer_base, (list, tuple)) else int(peer_base)
+
+    # --- the decode fast path ------------------------------------------------ #
+    def _try_fused(self, query, kv_cache, attn_metadata):
+        """O shaped [num_seqs, H, D] from the multi-GPU op, or None to signal fallback."""
+        if self._peer_cache is None or attn_metadata is None:
+            return None
+        try:
+            bt = getattr(attn_metadata, "block_table", None)
+            seq_lens = getattr(attn_metadata, "seq_lens", None)
+            if bt is None or seq_lens is None or kv_cache is None or kv_cache.dim() != 5:
+                return None
+            if getattr(attn_metadata, "use_cascade", False):
+                return None
+            q = query
+            if q.dim() == 2:                               # a single [H, D] token
+                q = q.unsqueeze(0)
+            if q.dim() != 3:
+                return None
+            n_act = getattr(attn_metadata, "num_actual_tokens", q.shape[0])
+            q = q[:n_act]
+            num_tokens, H, D = q.shape
+            bt2 = bt if bt.dim() == 2 else bt.unsqueeze(0)
+            num_seqs = bt2.size(0)
+            max_q = getattr(attn_metadata, "max_query_len", 1)
+            if D != 128 or num_tokens != num_seqs or max_q != 1:
+                return None                                # prefill / chunked batch: defer
+            if q.dtype not in (torch.float16, torch.bfloat16) or kv_cache.dtype != q.dtype:
+                return None                                # fp8 caches of vLLM use other scales
+            scale = self._scale_override or getattr(self, "scale", None) or 1.0 / math.sqrt(D)
+            return paged_cfk_decode(q, kv_cache, self._peer_cache, bt2, seq_lens[:num_seqs],
+                                    self._peer_base, scale=float(scale), splits=self._splits)
+        except Exception as e:  # noqa: BLE001 - any surprise -> safe fallback
+            logger.warning("PeerKV fused decode declined: %s", e)
+            return None
+
+    # --- vLLM hook ------------------------------------------------------------ #
+    def forward(self, layer, query, key, value, kv_cache, attn_metadata, output=None,
+                output_scale=None, output_block_scale=None):
+        O = None
+        if output_scale is None and output_block_scale is None:
+            O = self._try_fused(query, kv_cache, attn_metadata)
+        if O is None:
+            self.fallback_calls += 1
+            return super().forward(layer, query, key, value, kv_cache, attn_metadata, output,
+                                   output_scale, output_block_scale)
+        self.fused_calls += 1
+        if output is not None:
+            n = O.shape[0]                                  # rows past n are vLLM's padding
+            flat = output if query.dim() != 2 else output.unsqueeze(0)
+            flat[:n].reshape(n, -1).copy_(O.reshape(n, -1).to(output.dtype))
+            return output
+        O = O[0] if query.dim() == 2 else O
+        return O.to(query.dtype)
+
+
+def register_peerkv_fused() -> bool:
+    """Route FlashAttentionBackend.get_impl_cls to PeerKVFusedAttentionImpl; True if patched."""
+    from .register import install_cfk
+    return install_cfk()
