@@ -104,7 +104,7 @@ class PeerKVFusedAttentionImpl(FlashAttentionImpl):
         if output is not None:
             n = O.shape[0]                                  # rows past n are vLLM's padding
             flat = output if query.dim() != 2 else output.unsqueeze(0)
-            flat[:n].reshape(n, -1).copy_(O.reshape(n, -1).to(output.dtype))
+            flat[:n].view(n, -1).copy_(O.reshape(n, -1).to(output.dtype))
             return output
         O = O[0] if query.dim() == 2 else O
         return O.to(query.dtype)

@@ -1,0 +1,246 @@
+"""Placement and operating-point logic of the compute-follows-KV path, re-expressed
+for N uniform B200 peers behind an NVSwitch.
+
+Mirrors, for this path only, PeerKV's host-side cost helpers and selector:
+
+  partial_bytes, balanced_partition            umallm/multigpu.py:351-359, 362-377
+  PeerKVCostModel.decode_step_parallel_us      umallm/multigpu.py:191-215
+  PeerKVCostModel.max_context_for_slo_parallel umallm/multigpu.py:217-239
+  OperatingPoint, PeerState, select_point,
+  enforce_do_no_harm (the CFK-relevant rules)  umallm/elastic_policy.py:56-62, 261-284, 318-365
+
+The reference's constants are dual-A100 measurements (773 / 273 GB/s, 12-24 us set-up).
+The defaults here are what this library measures on B200 (effective KV read bandwidth
+of the decode kernel, cost of one exchange); `PeerKVCostModel.calibrate` refits them
+from two timed single-GPU points and one N-GPU point, the recipe of
+umallm/runtime/calibration.py:76-148.
+
+The page -> GPU maps themselves are made on the device (`pkv_split_block_table`,
+group.PeerGroup.split_table); `PagePlacer` is the allocation-time counterpart that
+decides where a NEW page goes.
+"""
+from __future__ import annotations
+
+import enum
+import math
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+# measured with this library on B200 (bf16, Hkv 8, D 128, 16-token pages)
+B200_KV_READ_GBPS = 7000.0       # decode kernel, >= 4 GiB per GPU
+B200_NVLINK_GBPS = 770.0         # per direction per GPU, measured peer copy
+B200_KERNEL_FIXED_US = 10.0      # launch + pipeline fill + split-K tail of one shard kernel
+B200_EXCHANGE_US = 18.0          # q publish + flag hops + final merge, all peers together
+B200_HBM_BYTES = 180 * 1024 ** 3
+
+
+def partial_bytes(heads: int, head_dim: int, lse_bytes: int = 4, o_bytes: int = 2) -> int:
+    """Bytes of one decode-step partial (O + lse) exchanged per remote shard; independent
+    of the KV size.  Defaults as in the reference (fp16 O); this library sends fp32 O
+    (`o_bytes=4`)."""
+    return heads * head_dim * o_bytes + heads * lse_bytes
+
+
+def balanced_partition(n_blocks: int, hbm_bw_gbps_per_device: Sequence[float]) -> List[int]:
+    """Blocks per device in proportion to its HBM bandwidth (equal GPUs: an even split,
+    the optimum); floors first, the remainder handed out one block at a time from
+    device 0."""
+    w = [float(b) for b in hbm_bw_gbps_per_device]
+    tot = sum(w) or 1.0
+    share = [int(n_blocks * x / tot) for x in w]
+    for k in range(n_blocks - sum(share)):
+        share[k % len(share)] += 1
+    return share
+
+
+@dataclass
+class PeerKVCostModel:
+    """step = compute + max_d(c_kernel + bytes_d / beta_hbm) + exchange(n_remote)."""
+    hbm_gbps: float = B200_KV_READ_GBPS
+    nvlink_gbps: float = B200_NVLINK_GBPS
+    kernel_fixed_us: float = B200_KERNEL_FIXED_US
+    exchange_us: float = B200_EXCHANGE_US
+
+    def decode_step_parallel_us(self, blocks_per_device: Sequence[int], block_bytes: int,
+                                compute_us: float = 0.0, part_bytes: Optional[int] = None,
+                                heads: int = 0, head_dim: int = 0) -> float:
+        bpd = [int(n) for n in blocks_per_device if int(n) > 0]
+        if not bpd:
+            return compute_us
+        reads = [self.kernel_fixed_us + n * block_bytes / (self.hbm_gbps * 1e3) for n in bpd]
+        if part_bytes is None:
+            part_bytes = partial_bytes(heads, head_dim) if (heads and head_dim) else 2080
+        n_remote = max(0, len(bpd) - 1)
+        # one latency-bound exchange for all peers (NVSwitch: peers do not share a link),
+        # plus the bytes that land on the home GPU's ingress
+        transfer = (self.exchange_us + n_remote * part_bytes / (self.nvlink_gbps * 1e3)) if n_remote else 0.0
+        return compute_us + max(reads) + transfer
+
+    def max_context_for_slo_parallel(self, deadline_us: float, block_bytes: int, n_devices: int = 2,
+                                     compute_us: float = 0.0, attn_us: float = 0.0,
+                                     part_bytes: int = 2080) -> dict:
+        transfer = (self.exchange_us + (n_devices - 1) * part_bytes / (self.nvlink_gbps * 1e3)) \
+            if n_devices > 1 else 0.0
+        budget = deadline_us - compute_us - attn_us - transfer - self.kernel_fixed_us
+        if budget <= 0:
+            return {"feasible": False, "max_blocks": 0, "max_blocks_per_device": 0, "n_devices": n_devices}
+        per_dev = budget * self.hbm_gbps * 1e3 / block_bytes
+        return {"feasible": True, "max_blocks": int(n_devices * per_dev),
+                "max_blocks_per_device": int(per_dev), "n_devices": n_devices,
+                "speedup_vs_single": float(n_devices)}
+
+    @classmethod
+    def calibrate(cls, single_pts: dict, multi_pt, n_devices: int) -> "PeerKVCostModel":
+        """single_pts = {bytes: us} (>= 2 single-GPU timings), multi_pt = (total_bytes, us)
+        on n_devices with an even split.  Fits beta_hbm and the kernel's fixed cost from
+        the single-GPU line and the exchange cost from the multi-GPU point."""
+        if len(single_pts) < 2:
+            raise ValueError("calibrate needs >= 2 single-GPU anchors")
+        (b1, t1), (b2, t2) = sorted(single_pts.items())[:2]
+        if b1 == b2:
+            raise ValueError("degenerate anchors: equal sizes")
+        slope = (t2 - t1) / (b2 - b1)
+        if slope <= 0:
+            raise ValueError("non-physical anchors: time does not grow with bytes; remeasure")
+        m = cls(hbm_gbps=1e-3 / slope, kernel_fixed_us=max(0.0, t1 - slope * b1))
+        tb, tt = multi_pt
+        m.exchange_us = max(0.0, tt - m.kernel_fixed_us - (tb / n_devices) * slope)
+        return m
+
+
+class OperatingPoint(enum.Enum):
+    SINGLE = "single"                   # the whole context on the query's GPU
+    CFK = "compute_follows_kv"          # KV sharded over peers, partials exchanged
+    INFEASIBLE = "infeasible"
+
+
+@dataclass
+class PeerState:
+    """Live state of the peer GPUs at admission time (umallm/elastic_policy.py:77-82)."""
+    n_peers: int = 7
+    hbm_free_bytes: int = B200_HBM_BYTES          # per peer, available to KV
+    compute_idle: bool = True                     # may the peers lend attention compute?
+    nvlink_bw_gbps: float = B200_NVLINK_GBPS      # 0 => link down / degraded
+
+
+@dataclass
+class Decision:
+    point: OperatingPoint
+    predicted_us: float
+    admissible: set = field(default_factory=set)
+    meets_deadline: bool = True
+    reason: str = ""
+
+
+class DoNoHarmViolation(RuntimeError):
+    """A chosen operating point would break a do-no-harm rule."""
+
+
+def admissible_points(kv_bytes: int, local_free_bytes: int, peer: PeerState) -> set:
+    pts = set()
+    if kv_bytes <= local_free_bytes:
+        pts.add(OperatingPoint.SINGLE)
+    n = peer.n_peers + 1
+    share = math.ceil(kv_bytes / n)
+    if peer.n_peers > 0 and peer.compute_idle and peer.nvlink_bw_gbps > 0 \
+            and share <= peer.hbm_free_bytes and share <= local_free_bytes:
+        pts.add(OperatingPoint.CFK)
+    return pts
+
+
+def select_point(kv_bytes: int, local_free_bytes: int, peer: PeerState,
+                 model: Optional[PeerKVCostModel] = None, deadline_us: Optional[float] = None,
+                 block_bytes: int = 65536) -> Decision:
+    """Pick the admissible point with the lowest predicted attention time per layer;
+    flag an SLO miss instead of refusing (umallm/elastic_policy.py:261-284)."""
+    model = model or PeerKVCostModel()
+    adm = admissible_points(kv_bytes, local_free_bytes, peer)
+    if not adm:
+        return Decision(OperatingPoint.INFEASIBLE, math.inf, adm, False, "no admissible point")
+    blocks = math.ceil(kv_bytes / block_bytes)
+    preds = {}
+    if OperatingPoint.SINGLE in adm:
+        preds[OperatingPoint.SINGLE] = model.decode_step_parallel_us([blocks], block_bytes)
+    if OperatingPoint.CFK in adm:
+        split = balanced_partition(blocks, [model.hbm_gbps] * (peer.n_peers + 1))
+        preds[OperatingPoint.CFK] = model.decode_step_parallel_us(split, block_bytes, heads=32, head_dim=128)
+    best = min(preds, key=preds.get)
+    why = []
+    if OperatingPoint.SINGLE not in adm:
+        why.append("context does not fit one GPU")
+    if OperatingPoint.CFK not in adm:
+        why.append("peers busy, full or unreachable -> single GPU only")
+    meets = deadline_us is None or preds[best] <= deadline_us
+    return Decision(best, preds[best], adm, meets, "; ".join(why) or "fastest admissible")
+
+
+def enforce_do_no_harm(point: OperatingPoint, kv_bytes: int, local_free_bytes: int,
+                       peer: PeerState, model: Optional[PeerKVCostModel] = None,
+                       block_bytes: int = 65536) -> OperatingPoint:
+    """Rules of umallm/elastic_policy.py:318-365 that concern this path:
+    R1-busy (peers computing -> CFK forbidden), R1-route (link down -> CFK forbidden),
+    R1-fit, restated for a path that can be FASTER than one GPU: a context that fits one
+    GPU may still be sharded, but only when the model predicts it is not slower."""
+    model = model or PeerKVCostModel()
+    if point is OperatingPoint.CFK:
+        if not peer.compute_idle:
+            raise DoNoHarmViolation("R1-busy: peer compute-busy, CFK forbidden")
+        if peer.nvlink_bw_gbps <= 0 or peer.n_peers <= 0:
+            raise DoNoHarmViolation("R1-route: no usable NVLink path to a peer, CFK forbidden")
+        if kv_bytes <= local_free_bytes:
+            blocks = math.ceil(kv_bytes / block_bytes)
+            single = model.decode_step_parallel_us([blocks], block_bytes)
+            split = balanced_partition(blocks, [model.hbm_gbps] * (peer.n_peers + 1))
+            cfk = model.decode_step_parallel_us(split, block_bytes, heads=32, head_dim=128)
+            if cfk > single:
+                raise DoNoHarmViolation(
+                    f"R1-fit: fits one GPU and sharding is predicted slower ({cfk:.1f} > {single:.1f} us)")
+    if point is OperatingPoint.SINGLE and kv_bytes > local_free_bytes:
+        raise DoNoHarmViolation("SINGLE chosen but the context does not fit one GPU")
+    return point
+
+
+class PagePlacer:
+    """Allocation-time page -> (gpu, local id) decisions for a sharded KV pool.
+
+    policy 'round_robin': page p -> GPU p mod N (the batched benchmark configuration);
+    policy 'balanced': keep every GPU's page count proportional to its bandwidth
+    (`balanced_partition`), new pages going to the most under-filled GPU;
+    policy 'capacity_spill': fill GPUs in order up to their capacity, then spill on.
+    """
+
+    def __init__(self, n_gpus: int, policy: str = "round_robin",
+                 capacity_pages: Optional[Sequence[int]] = None,
+                 bandwidth_gbps: Optional[Sequence[float]] = None):
+        if policy not in ("round_robin", "balanced", "capacity_spill"):
+            raise ValueError(policy)
+        self.n, self.policy = n_gpus, policy
+        self.capacity = list(capacity_pages) if capacity_pages is not None else [1 << 62] * n_gpus
+        self.bw = list(bandwidth_gbps) if bandwidth_gbps is not None else [1.0] * n_gpus
+        self.used = [0] * n_gpus
+        self._next = 0
+
+    def place(self) -> tuple:
+        """Returns (gpu, local page id) for one new page."""
+        if self.policy == "round_robin":
+            for _ in range(self.n):
+                g = self._next % self.n
+                self._next += 1
+                if self.used[g] < self.capacity[g]:
+                    break
+            else:
+                raise MemoryError("every GPU is at capacity")
+        elif self.policy == "capacity_spill":
+            g = next((i for i in range(self.n) if self.used[i] < self.capacity[i]), None)
+            if g is None:
+                raise MemoryError("every GPU is at capacity")
+        else:
+            tot = sum(self.used) + 1
+            want = balanced_partition(tot, self.bw)
+            cands = [i for i in range(self.n) if self.used[i] < self.capacity[i]]
+            if not cands:
+                raise MemoryError("every GPU is at capacity")
+            g = max(cands, key=lambda i: (want[i] - self.used[i], -i))
+        local = self.used[g]
+        self.used[g] += 1
+        return g, local
