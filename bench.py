@@ -281,6 +281,7 @@ def build_workload(name, context, N, rank, dev):
            "l2_policy": "inputs larger than L2 (KV per GPU >= 1 GiB, read once per step)"}
     return dict(B=B, HQ=HQ, HKV=HKV, pool=pool, scales=scales, tab=my_tab, len=my_len,
                 bytes_per_token=bpt, total_tokens=int(lens.sum()), max_rank_tokens=max(rank_tokens),
+                rank_tokens=rank_tokens,
                 q_dtype=torch.bfloat16, dtype="bf16" if fmt == "bf16" else "f16",
                 config=cfg)
 
@@ -363,6 +364,8 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    rank_ms = []
+
     def timed(fn, n):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
@@ -375,8 +378,10 @@ def main():
         ms = e0.elapsed_time(e1)
         if N > 1:
             t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t)
+            allt = [torch.zeros_like(t) for _ in range(N)]
+            dist.all_gather(allt, t)
+            rank_ms[:] = [float(x) / n for x in allt]
+            ms = max(float(x) for x in allt)
         return ms
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
@@ -387,6 +392,7 @@ def main():
         sampler.start()
     total_ms = timed(step, args.steps)
     ms_per_step = total_ms / args.steps
+    step_rank_ms = list(rank_ms)
     # keep the GPU under the same load long enough for the clock sampler to see it
     soak_steps = 0
     if total_ms < 1500.0 and not args.lean:
@@ -454,6 +460,7 @@ def main():
             "gpu_launches": launches_per_step * args.steps,
             "clocks": dict(clocks or {}, note=f"sampled over the timed steps plus {soak_steps} more identical steps"),
             "device_status": status,
+            "rank_ms_per_step": step_rank_ms, "rank_kv_bytes": [t * bytes_per_token for t in wl["rank_tokens"]],
         }
         if N == 1 and not args.no_cpu_baseline and not args.lean and args.workload == "paged-bf16":
             cores = os.cpu_count() or 1

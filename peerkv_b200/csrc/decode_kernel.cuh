@@ -179,65 +179,66 @@ __device__ __forceinline__ void fold_slot(float& M, float& L, float4& acc, float
 // heads qh0.. and writes their rows; each lane owns 4 of the 128 dims.  c1 < c0 means
 // the shard holds no token of the sequence.  This runs in the kernel's tail, where a
 // dependent chain of L2 round trips is what costs, so each step first issues all
-// loads of four slots x four heads (statistics and rows, none depending on another
-// and no shuffle in between) and only then does the arithmetic.
-__device__ __forceinline__ void combine_heads4(const DecodeParams& p, int b, int qh0, int nh,
-                                               int c0, int c1, int lane) {
-  float4 acc[4];
-  float M[4], L[4];
+// loads of NS slots x NH heads (statistics and rows, none depending on another and no
+// shuffle in between) and only then does the arithmetic.
+template <int NH, int NS>   // heads per pass, slots (or peer parts) loaded per round
+__device__ __forceinline__ void combine_heads(const DecodeParams& p, int b, int qh0, int nh,
+                                              int c0, int c1, int lane) {
+  float4 acc[NH];
+  float M[NH], L[NH];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < NH; ++i) {
     acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     M[i] = -INFINITY; L[i] = 0.f;
   }
   const float2* ml2 = reinterpret_cast<const float2*>(p.part_ml);
-  for (int base = c0; base <= c1; base += 4) {
-    float2 ml[4][4];
-    float4 os[4][4];
+  for (int base = c0; base <= c1; base += NS) {
+    float2 ml[NS][NH];
+    float4 os[NS][NH];
 #pragma unroll
-    for (int jj = 0; jj < 4; ++jj) {
+    for (int jj = 0; jj < NS; ++jj) {
       const int c = min(base + jj, c1);           // clamped: a valid row even past the end
       const int64_t row0 = (int64_t)c * p.n_q_heads + qh0;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < NH; ++i) {
         const int64_t row = row0 + (i < nh ? i : 0);
         ml[jj][i] = __ldcg(ml2 + row);
         os[jj][i] = __ldcg(reinterpret_cast<const float4*>(p.part_o + row * kHeadDim) + lane);
       }
     }
 #pragma unroll
-    for (int jj = 0; jj < 4; ++jj) {
+    for (int jj = 0; jj < NS; ++jj) {
       if (base + jj <= c1) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) fold_slot(M[i], L[i], acc[i], ml[jj][i].x, ml[jj][i].y, os[jj][i]);
+        for (int i = 0; i < NH; ++i) fold_slot(M[i], L[i], acc[i], ml[jj][i].x, ml[jj][i].y, os[jj][i]);
       }
     }
   }
   // The peers' shard partials are slots too: (m = lse * log2 e, l = 1, o = O normalised).
-  for (int r0 = 0; r0 < p.mg_n; r0 += 4) {
-    float ls[4][4];
-    float4 os[4][4];
+  for (int r0 = 0; r0 < p.mg_n; r0 += NS) {
+    float ls[NS][NH];
+    float4 os[NS][NH];
 #pragma unroll
-    for (int jj = 0; jj < 4; ++jj) {
+    for (int jj = 0; jj < NS; ++jj) {
       const int r = min(r0 + jj, p.mg_n - 1);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < NH; ++i) {
         const int64_t row = (int64_t)b * p.n_q_heads + qh0 + (i < nh ? i : 0);
         ls[jj][i] = __ldcg(p.mg_lse + r * p.mg_lse_stride + row);
         os[jj][i] = __ldcg(reinterpret_cast<const float4*>(p.mg_o + r * p.mg_o_stride + row * kHeadDim) + lane);
       }
     }
 #pragma unroll
-    for (int jj = 0; jj < 4; ++jj) {
+    for (int jj = 0; jj < NS; ++jj) {
       if (r0 + jj < p.mg_n && r0 + jj != p.mg_self) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < NH; ++i)
           fold_slot(M[i], L[i], acc[i], ls[jj][i] * 1.4426950408889634f, 1.f, os[jj][i]);
       }
     }
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < NH; ++i) {
     if (i < nh) {
       const float inv = L[i] > 0.f ? 1.f / L[i] : 0.f;
       float4 v = acc[i];
@@ -252,10 +253,16 @@ __device__ __forceinline__ void combine_heads4(const DecodeParams& p, int b, int
   }
 }
 
+// LIGHT: the CTA runs two consumer warps per head and has few registers per thread:
+// one head per pass, eight slots per round (the 4x4 form would spill and serialise).
+template <bool LIGHT>
 __device__ __forceinline__ void combine_group(const DecodeParams& p, int b, int qh0, int nq,
                                               int c0, int c1, int lane) {
-  combine_heads4(p, b, qh0, min(nq, 4), c0, c1, lane);
-  if (nq > 4) combine_heads4(p, b, qh0 + 4, nq - 4, c0, c1, lane);
+  if constexpr (LIGHT) {
+    for (int i = 0; i < nq; ++i) combine_heads<1, 8>(p, b, qh0 + i, 1, c0, c1, lane);
+  } else {
+    for (int i = 0; i < nq; i += 4) combine_heads<4, 4>(p, b, qh0 + i, min(4, nq - i), c0, c1, lane);
+  }
 }
 
 // Bounded wait of one warp for the peers' completion flags (lane r polls rank r).
@@ -411,23 +418,27 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
 
   if (warp == kServiceWarp) {
     // ---------------------------- service warp ---------------------------- //
-    // Sequences with no token in this shard have no CTA: CTA 0 of each head block
-    // writes their rows (neutral, or the merge of the peers' rows on the home GPU).
-    if (p.fuse && blockIdx.x == 0) {
-      const int qh0 = head0 * p.group, nqh = heads_here * p.group;
-      int n_empty = 0;
+    // Sequences with no token in this shard have no CTA of their own.  Their rows
+    // (neutral, or -- on the home GPU -- the merge of the peers' rows) are written by the
+    // service warps: unit (empty sequence e, kv-head h) goes to the service warp of CTA
+    // (e * heads_here + h) mod gridDim.x, so a ragged batch whose sequences mostly live on
+    // other GPUs does not serialise its merge in one warp.
+    if (p.fuse) {
+      int n_done = 0, unit = 0;
       bool peers_ok = true, waited = false;
       for (int b = 0; b < p.batch; ++b) {
         if (prefix[b + 1] != prefix[b]) continue;
-        ++n_empty;
-        if (p.mg_n > 0 && !waited) { peers_ok = wait_peer_flags(p, lane); waited = true; }
-        if (peers_ok)
-          for (int i = 0; i < nqh; i += 4) combine_heads4(p, b, qh0 + i, min(4, nqh - i), 0, -1, lane);
+        for (int h = 0; h < heads_here; ++h, ++unit) {
+          if (unit % (int)gridDim.x != (int)blockIdx.x) continue;
+          if (p.mg_n > 0 && !waited) { peers_ok = wait_peer_flags(p, lane); waited = true; }
+          if (peers_ok) combine_group<(WPH > 1)>(p, b, (head0 + h) * p.group, p.group, 0, -1, lane);
+          ++n_done;
+        }
       }
-      if (n_empty && p.done_flag) {
+      if (n_done && p.done_flag) {
         __threadfence_system();
         __syncwarp();
-        if (lane == 0) count_done(p, n_empty * heads_here, units);
+        if (lane == 0) count_done(p, n_done, units);
       }
     }
     return;
@@ -836,7 +847,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       last = __shfl_sync(0xffffffffu, last, 0);
       if (last && p.mg_n > 0) last = wait_peer_flags(p, lane) ? 1 : 0;   // home: peers' rows needed
       if (last) {
-        combine_group(p, s, kvh * G, G, slot_lo, slot_hi, lane);
+        combine_group<(WPH > 1)>(p, s, kvh * G, G, slot_lo, slot_hi, lane);
         if (p.done_flag) {
           __threadfence_system();
           __syncwarp();
