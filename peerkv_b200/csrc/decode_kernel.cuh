@@ -325,7 +325,10 @@ struct SmemLayout {
 // 1-byte codes -> fp16 pairs, exactly.  int8: bias the byte to unsigned, plant it in the
 // mantissa of 1024.0 (0x6400 | u = 1024 + u) and subtract 1152; e4m3: the hardware cvt.
 // `SEL_A` / `SEL_B` pick which two bytes of `r` form each pair (prmt selectors).
-template <bool FP8>
+// UNBIAS = false (int8 only) leaves every value 1152 too large; the caller takes
+// 1152 * sum(q) off the dot product instead, which is exact in the fp32 accumulator for
+// the 128-term sums it is used on and saves two instructions per register.
+template <bool FP8, bool UNBIAS = true>
 __device__ __forceinline__ void codes_to_half2(uint32_t r, uint32_t sel_a, uint32_t sel_b,
                                                uint32_t& a, uint32_t& b) {
   if constexpr (FP8) {
@@ -339,9 +342,11 @@ __device__ __forceinline__ void codes_to_half2(uint32_t r, uint32_t sel_a, uint3
     const uint32_t x = r ^ 0x80808080u;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(a) : "r"(x), "r"(0x64646464u), "r"(sel_a));
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(b) : "r"(x), "r"(0x64646464u), "r"(sel_b));
-    const uint32_t bias = 0x64806480u;   // 1152.0 twice
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(a) : "r"(a), "r"(bias));
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(b) : "r"(b), "r"(bias));
+    if constexpr (UNBIAS) {
+      const uint32_t bias = 0x64806480u;   // 1152.0 twice
+      asm("sub.f16x2 %0, %1, %2;" : "=r"(a) : "r"(a), "r"(bias));
+      asm("sub.f16x2 %0, %1, %2;" : "=r"(b) : "r"(b), "r"(bias));
+    }
   }
 }
 
@@ -579,9 +584,11 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
   const uint32_t vrow_off = vrow * 128, vx = vrow & 7;
 
   bool q_ready = (p.q_flag == nullptr);
+  const bool ps16 = (p.page_size % kTileTok) == 0;
 
   int s = find_seq(prefix, p.batch, g0);
-  int it = 0;
+  int it = 0, stage = 0;           // tile counter of this CTA and its ring slot / phase
+  uint32_t ph = 0;
   for (int gt = g0; gt < g1;) {
     while (prefix[s + 1] <= gt) ++s;
     const int seg_end = min(g1, prefix[s + 1]);
@@ -633,19 +640,41 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
         }
       }
     }
+    // int8 pools: K codes enter the MMA as (code + 1152); 1152 * sum_d q[head][d] comes
+    // off each score.  The sums are taken over the fp16 values the MMA really uses.
+    float qb0 = 0.f, qb1 = 0.f;          // for score columns (q heads) 2t and 2t+1
+    if constexpr (KVT == kKvInt8) {
+      float qs = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const __half2 x = *reinterpret_cast<const __half2*>(&qf[ks][0]);
+        const __half2 y = *reinterpret_cast<const __half2*>(&qf[ks][1]);
+        qs += (__low2float(x) + __high2float(x)) + (__low2float(y) + __high2float(y));
+      }
+      qs += __shfl_xor_sync(0xffffffffu, qs, 1);
+      qs += __shfl_xor_sync(0xffffffffu, qs, 2);      // all of head g's 128 dims
+      qb0 = 1152.f * __shfl_sync(0xffffffffu, qs, (2 * t) * 4);
+      qb1 = 1152.f * __shfl_sync(0xffffffffu, qs, (2 * t + 1) * 4);
+    }
     float o[8][4];
 #pragma unroll
     for (int j = 0; j < 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const int n_seq_tiles = prefix[s + 1] - prefix[s];
 
-    for (int ti = gt - prefix[s]; gt < seg_end; ++gt, ++ti, ++it) {
-      if (WPH > 1 && (it % WPH) != par) continue;   // the sibling warp's tile
-      const int stage = it % NSTAGE;
-      const uint32_t ph = (it / NSTAGE) & 1;
-      // valid tokens of this tile
-      const int pj = ti / p.tiles_per_page;
-      const int tok0 = (ti - pj * p.tiles_per_page) * kTileTok;
-      const int valid = min(kTileTok, min(p.page_size - tok0, len - pj * p.page_size - tok0));
+    for (int ti = gt - prefix[s]; gt < seg_end;
+         ++gt, ++ti, ++it, stage = (stage + 1 == NSTAGE ? 0 : stage + 1), ph ^= (stage == 0)) {
+      if (WPH > 1 && (it & (WPH - 1)) != par) continue;   // the sibling warp's tile
+      // valid tokens of this tile: 16 except on a sequence's last tile (pages that are a
+      // multiple of 16 tokens), else from the tile's position inside its page
+      int valid = kTileTok;
+      if (ps16) {
+        if (ti == n_seq_tiles - 1) valid = len - ti * kTileTok;
+      } else {
+        const int pj = ti / p.tiles_per_page;
+        const int tok0 = (ti - pj * p.tiles_per_page) * kTileTok;
+        valid = min(kTileTok, min(p.page_size - tok0, len - pj * p.page_size - tok0));
+      }
       const uint32_t sk = sbase + stage * L::kSlotBytes + koff;
       const uint32_t sv = sbase + stage * L::kSlotBytes + voff;
 
@@ -667,11 +696,12 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
             const uint32_t chunk = (kp << 1) | kcsel;
             ldmatrix_x4(r, sk + krow_off + ((chunk ^ kx) << 4));
             // r0: tok g, chunk 2kp; r1: tok g+8, chunk 2kp; r2, r3: chunk 2kp+1
-            codes_to_half2<KVT == kKvFp8>(r[0], kQuantSelK0<KVT == kKvFp8>(), kQuantSelK1<KVT == kKvFp8>(), a[0], a[2]);
-            codes_to_half2<KVT == kKvFp8>(r[1], kQuantSelK0<KVT == kKvFp8>(), kQuantSelK1<KVT == kKvFp8>(), a[1], a[3]);
+            constexpr bool F8 = KVT == kKvFp8;
+            codes_to_half2<F8, false>(r[0], kQuantSelK0<F8>(), kQuantSelK1<F8>(), a[0], a[2]);
+            codes_to_half2<F8, false>(r[1], kQuantSelK0<F8>(), kQuantSelK1<F8>(), a[1], a[3]);
             mma_16816<false>(sa, a, qf[2 * kp][0], qf[2 * kp][1]);
-            codes_to_half2<KVT == kKvFp8>(r[2], kQuantSelK0<KVT == kKvFp8>(), kQuantSelK1<KVT == kKvFp8>(), a[0], a[2]);
-            codes_to_half2<KVT == kKvFp8>(r[3], kQuantSelK0<KVT == kKvFp8>(), kQuantSelK1<KVT == kKvFp8>(), a[1], a[3]);
+            codes_to_half2<F8, false>(r[2], kQuantSelK0<F8>(), kQuantSelK1<F8>(), a[0], a[2]);
+            codes_to_half2<F8, false>(r[3], kQuantSelK0<F8>(), kQuantSelK1<F8>(), a[1], a[3]);
             mma_16816<false>(sb, a, qf[2 * kp + 1][0], qf[2 * kp + 1][1]);
           }
           // per-token K scales (rows g and g+8 of the score tile)
@@ -684,8 +714,8 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
           const __half* ksc = reinterpret_cast<const __half*>(sgen + L::kScaleOff + stage * L::kScaleSlot);
           const float k0 = __half2float(ksc[g * scale_stride + hh]) * p.scale_log2;
           const float k1 = __half2float(ksc[(g + 8) * scale_stride + hh]) * p.scale_log2;
-          sc[0] = (sa[0] + sb[0]) * k0; sc[1] = (sa[1] + sb[1]) * k0;
-          sc[2] = (sa[2] + sb[2]) * k1; sc[3] = (sa[3] + sb[3]) * k1;
+          sc[0] = (sa[0] + sb[0] - qb0) * k0; sc[1] = (sa[1] + sb[1] - qb1) * k0;
+          sc[2] = (sa[2] + sb[2] - qb0) * k1; sc[3] = (sa[3] + sb[3] - qb1) * k1;
         } else {
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
@@ -774,11 +804,11 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
             // r0: toks 0-7, chunk 2jp; r1: toks 8-15, chunk 2jp; r2, r3: chunk 2jp+1
             codes_to_half2<KVT == kKvFp8>(r[0], kQuantSelV0<KVT == kKvFp8>(), kQuantSelV1<KVT == kKvFp8>(), a[0], a[1]);
             codes_to_half2<KVT == kKvFp8>(r[1], kQuantSelV0<KVT == kKvFp8>(), kQuantSelV1<KVT == kKvFp8>(), a[2], a[3]);
-            a[0] &= mk01; a[1] &= mk01; a[2] &= mk23; a[3] &= mk23;
+            if (valid < kTileTok) { a[0] &= mk01; a[1] &= mk01; a[2] &= mk23; a[3] &= mk23; }
             mma_16816<false>(o[2 * jp], a, b0, b1);
             codes_to_half2<KVT == kKvFp8>(r[2], kQuantSelV0<KVT == kKvFp8>(), kQuantSelV1<KVT == kKvFp8>(), a[0], a[1]);
             codes_to_half2<KVT == kKvFp8>(r[3], kQuantSelV0<KVT == kKvFp8>(), kQuantSelV1<KVT == kKvFp8>(), a[2], a[3]);
-            a[0] &= mk01; a[1] &= mk01; a[2] &= mk23; a[3] &= mk23;
+            if (valid < kTileTok) { a[0] &= mk01; a[1] &= mk01; a[2] &= mk23; a[3] &= mk23; }
             mma_16816<false>(o[2 * jp + 1], a, b0, b1);
           }
         } else {
@@ -787,7 +817,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
             uint32_t a[4];
             const uint32_t chunk = ((j & 3) << 1) | vcsel;
             ldmatrix_x4_trans(a, sv + (j >> 2) * 2048 + vrow_off + ((chunk ^ vx) << 4));
-            a[0] &= mk01; a[1] &= mk01; a[2] &= mk23; a[3] &= mk23;
+            if (valid < kTileTok) { a[0] &= mk01; a[1] &= mk01; a[2] &= mk23; a[3] &= mk23; }
             mma_16816<BF16>(o[j], a, b0, b1);
           }
         }
