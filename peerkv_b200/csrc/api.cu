@@ -93,6 +93,8 @@ struct pkv_shard {
   unsigned int* done_counter = nullptr;
   unsigned int* counters = nullptr;  // [n_counter_words]: 64 global words, then per (sequence, kv-head)
   size_t n_counter_words = 0;
+  uint32_t* obs[2] = {nullptr, nullptr};   // per-CTA timings of the last launch / for the next one
+  int obs_parity = 0;
   std::vector<MapEntry> maps;
   uint64_t stamp = 0;
   bool attr_set = false;
@@ -288,6 +290,8 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   const pkv_kv_view& kv = a->kv;
   const int n_hb = (kv.n_kv_heads + pkv::kHeadsPerCta - 1) / pkv::kHeadsPerCta;
   const int n_cta_x = s->num_sms / n_hb > 0 ? s->num_sms / n_hb : 1;
+  if (n_cta_x > pkv::kMaxCtas)
+    return fail(PKV_E_UNSUPPORTED, "%d CTAs per head block exceed the kernel's %d", n_cta_x, pkv::kMaxCtas);
 
   pkv::DecodeParams p;
   memset(&p, 0, sizeof p);
@@ -322,6 +326,11 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   p.all_counter = s->counters;
   p.done_flag = lo.done_flag;
   p.done_epoch = lo.done_epoch;
+  if (s->obs[0] && n_cta_x <= pkv::kMaxCtas) {
+    p.obs_read = s->obs[s->obs_parity];
+    p.obs_write = s->obs[s->obs_parity ^ 1];
+    s->obs_parity ^= 1;
+  }
   if (lo.home) {
     pkv_exchange* x = lo.home;
     p.mg_n = x->world;
@@ -436,8 +445,11 @@ int pkv_shard_create(pkv_shard** out, int device, int max_batch, int n_q_heads) 
   if (e == cudaSuccess) e = cudaMalloc(&s->status, 256);
   if (e == cudaSuccess) e = cudaMemset(s->status, 0, 256);
   s->n_counter_words = (size_t)n_q_heads * max_batch + 64;   // n_kv_heads <= n_q_heads
-  if (e == cudaSuccess) e = cudaMalloc(&s->counters, s->n_counter_words * sizeof(unsigned int));
-  if (e == cudaSuccess) e = cudaMemset(s->counters, 0, s->n_counter_words * sizeof(unsigned int));
+  const size_t obs_words = 1 + 3 * pkv::kMaxCtas;
+  if (e == cudaSuccess) e = cudaMalloc(&s->counters, (s->n_counter_words + 2 * obs_words) * sizeof(unsigned int));
+  if (e == cudaSuccess) e = cudaMemset(s->counters, 0, (s->n_counter_words + 2 * obs_words) * sizeof(unsigned int));
+  s->obs[0] = s->counters + s->n_counter_words;
+  s->obs[1] = s->obs[0] + obs_words;
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
     pkv_shard_destroy(s);
@@ -810,13 +822,14 @@ constexpr int kStaticMaxQHeads = 64;
 constexpr int kStaticMaxSms = 192;
 constexpr int kStaticMaxDevices = 16;
 constexpr size_t kStaticSlots = (size_t)(kStaticMaxSms + kStaticMaxBatch) * pkv::kMaxWph;
-constexpr size_t kStaticWords = 128 + (size_t)kStaticMaxBatch * kStaticMaxQHeads;
+constexpr size_t kStaticObsWords = 1 + 3 * pkv::kMaxCtas;
+constexpr size_t kStaticWords = 128 + (size_t)kStaticMaxBatch * kStaticMaxQHeads;   // cleared per call
 
 // One copy per GPU that loads the library, held until the process exits (14.8 MB).
 // In host code these names are only handles for cudaGetSymbolAddress, never pointers.
 static __device__ __align__(256) float g_static_part_o[kStaticSlots * kStaticMaxQHeads * pkv::kHeadDim];
 static __device__ __align__(256) float g_static_part_ml[kStaticSlots * kStaticMaxQHeads * 2];
-static __device__ __align__(256) unsigned int g_static_words[kStaticWords];
+static __device__ __align__(256) unsigned int g_static_words[kStaticWords + 2 * kStaticObsWords];
 
 pkv_shard g_static_shard[kStaticMaxDevices];
 bool g_static_ready[kStaticMaxDevices];
@@ -852,6 +865,8 @@ int static_setup(int device) {
   s.done_counter = pw + 16;
   s.counters = pw + 64;                                // 64 global words, then per (sequence, kv-head)
   s.n_counter_words = kStaticWords - 64;
+  s.obs[0] = pw + kStaticWords;           // survive from call to call (not cleared)
+  s.obs[1] = s.obs[0] + kStaticObsWords;
   s.cache_maps = false;                                // tensor maps are encoded on the stack
   { int rc = set_kernel_attrs(); if (rc) return rc; }
   s.attr_set = true;

@@ -39,6 +39,7 @@ constexpr int kProducerWarps = 2;   // one feeds the K ring, one the V ring
 constexpr int kMaxWph = 2;
 __host__ __device__ constexpr int cta_threads(int wph) { return (kHeadsPerCta * wph + kProducerWarps + 1) * 32; }
 constexpr int kMaxBatch = 4096;
+constexpr int kMaxCtas = 256;       // CTAs along x (one per SM)
 
 constexpr uint32_t kPollLimit = 1u << 20;  // polls of mbarrier.try_wait before giving up
 
@@ -82,6 +83,10 @@ struct DecodeParams {
   unsigned int* all_counter;   // sequences finished, zero between launches
   uint64_t* done_flag;         // released with done_epoch when every sequence is out (may be P2P)
   uint64_t done_epoch;
+  // adaptive split of the tile list: per-CTA (duration ns, tiles, weight) of the previous
+  // launch on this shard; written for the next one.  Word 0 is the CTA count they refer to.
+  const uint32_t* obs_read;
+  uint32_t* obs_write;
   // home GPU only -- final merge in the tail: after a (sequence, kv-head) is combined locally
   // the same warp waits (bounded) for the peers' flags and folds their (O, lse) rows in.
   int mg_n;                    // partial slots (ranks); 0 = no merge
@@ -301,6 +306,87 @@ __device__ __forceinline__ void count_done(const DecodeParams& p, unsigned int n
   }
 }
 
+// Where each CTA's range of the flat tile list starts: bound[c] .. bound[c+1].
+// SMs do not stream at the same rate (the same ones are a few per cent slower launch
+// after launch), so an equal split leaves the slowest CTA running alone at the end.
+// Each launch therefore records, per CTA, how long its tiles took; the next launch on
+// the same shard splits the list in proportion to those rates (damped, clamped to
+// [0.5, 2]).  Small problems, a first launch, or a changed grid use the equal split, and
+// every CTA computes the same bounds from the same inputs.  Ends with __syncthreads().
+__device__ __forceinline__ void build_cta_bounds(int* bound, float* wtmp, int total, int n_cta,
+                                                 const uint32_t* obs) {
+  const int tid = threadIdx.x;
+  const bool adaptive = obs && obs[0] == (uint32_t)n_cta && total >= 8 * n_cta && n_cta <= kMaxCtas;
+  if (!adaptive) {
+    const int per = (total + n_cta - 1) / n_cta;
+    for (int c = tid; c <= n_cta; c += blockDim.x) {
+      bound[c] = min(total, c * per);
+      if (c < min(n_cta, kMaxCtas)) wtmp[c] = 1.f;
+    }
+    __syncthreads();
+    return;
+  }
+  // rates of the previous launch
+  for (int c = tid; c < n_cta; c += blockDim.x) {
+    const float dur = (float)obs[1 + 3 * c], tiles = (float)obs[2 + 3 * c];
+    wtmp[c] = (dur > 0.f && tiles > 0.f) ? tiles / dur : 0.f;
+  }
+  __syncthreads();
+  if (tid < 32) {
+    float sum = 0.f; int cnt = 0;
+    for (int c = tid; c < n_cta; c += 32) if (wtmp[c] > 0.f) { sum += wtmp[c]; ++cnt; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+    }
+    const float mean = cnt > 0 ? sum / cnt : 1.f;
+    // weight = half the weight used last time + half the observed relative rate
+    float carry = 0.f;
+    for (int base = 0; base < n_cta; base += 32) {
+      const int c = base + tid;
+      float w = 0.f;
+      if (c < n_cta) {
+        const float rel = wtmp[c] > 0.f ? wtmp[c] / mean : 1.f;
+        const float prev = __uint_as_float(obs[3 + 3 * c]);
+        const float pw = (prev > 0.25f && prev < 4.f) ? prev : 1.f;
+        w = fminf(fmaxf(0.5f * pw + 0.5f * rel, 0.5f), 2.f);
+        wtmp[c] = w;
+      }
+      float v = w;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float n = __shfl_up_sync(0xffffffffu, v, o);
+        if (tid >= o) v += n;
+      }
+      v += carry;
+      if (c < n_cta) reinterpret_cast<float*>(bound)[c + 1] = v;     // inclusive prefix, as float for now
+      carry = __shfl_sync(0xffffffffu, v, 31);
+    }
+    const float tot_w = carry;
+    __syncwarp();
+    for (int c = tid; c < n_cta; c += 32) {
+      const float cum = reinterpret_cast<float*>(bound)[c + 1];
+      int b = (int)((double)total * (double)cum / (double)tot_w);
+      b = min(max(b, 0), total);
+      if (c == n_cta - 1) b = total;
+      bound[c + 1] = b;
+    }
+    if (tid == 0) bound[0] = 0;
+  }
+  __syncthreads();
+}
+
+// The CTA whose range holds tile g: largest c with bound[c] <= g.
+__device__ __forceinline__ int find_cta(const int* bound, int n_cta, int g) {
+  int lo = 0, hi = n_cta;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (bound[mid] <= g) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
 // KV element kinds (the PKV_* dtype codes of the C ABI)
 constexpr int kKvF16 = 0, kKvBF16 = 1, kKvInt8 = 2, kKvFp8 = 3;
 
@@ -318,7 +404,9 @@ struct SmemLayout {
   static constexpr int kBarOff = kScaleOff + kScaleBytes;
   static constexpr int kNumBars = 2 * NSTAGE * kHeadsPerCta + 4 * NSTAGE;
   static constexpr int kAbortOff = kBarOff + kNumBars * 8;
-  static constexpr int kPrefixOff = kAbortOff + 16;
+  static constexpr int kBoundOff = kAbortOff + 16;                     // tile range bounds per CTA
+  static constexpr int kWeightOff = kBoundOff + (kMaxCtas + 1) * 4;    // split weights (floats)
+  static constexpr int kPrefixOff = kWeightOff + kMaxCtas * 4;
   static constexpr int kTotal = kPrefixOff + (kMaxBatch + 1) * 4 + 1024;  // +1024: manual alignment
 };
 
@@ -416,9 +504,21 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
   build_tile_prefix(prefix, p.seq_lens, p.batch, p.page_size, p.tiles_per_page);
 
   const int total = prefix[p.batch];
-  const int per = (total + p.n_cta_x - 1) / p.n_cta_x;
-  const int g0 = min(total, (int)blockIdx.x * per);
-  const int g1 = min(total, g0 + per);
+  int* bound = reinterpret_cast<int*>(sgen + L::kBoundOff);
+  float* cta_weight = reinterpret_cast<float*>(sgen + L::kWeightOff);
+  build_cta_bounds(bound, cta_weight, total, p.n_cta_x, p.obs_read);
+  const int g0 = bound[blockIdx.x];
+  const int g1 = bound[blockIdx.x + 1];
+  unsigned long long t_start;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_start));
+  if (p.obs_write && warp == 0 && lane == 0 && blockIdx.y == 0) {
+    if (blockIdx.x == 0) p.obs_write[0] = (uint32_t)p.n_cta_x;
+    if (g0 >= g1) {                       // nothing to time: keep the weight, no rate
+      p.obs_write[1 + 3 * blockIdx.x] = 0u;
+      p.obs_write[2 + 3 * blockIdx.x] = 0u;
+      p.obs_write[3 + 3 * blockIdx.x] = __float_as_uint(1.f);
+    }
+  }
   const unsigned int units = (unsigned int)p.batch * p.n_kv_heads;   // (sequence, kv-head) pairs
 
   if (warp == kServiceWarp) {
@@ -826,6 +926,14 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       if (lane == 0) mbar_arrive(empty(1, stage));
     }
 
+    if (gt >= g1 && p.obs_write && warp == 0 && lane == 0 && blockIdx.y == 0) {
+      // this CTA's tiles are done: what the next launch's split is computed from
+      unsigned long long t_end;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_end));
+      p.obs_write[1 + 3 * blockIdx.x] = (uint32_t)min(t_end - t_start, 0xffffffffull);
+      p.obs_write[2 + 3 * blockIdx.x] = (uint32_t)(g1 - g0);
+      p.obs_write[3 + 3 * blockIdx.x] = __float_as_uint(cta_weight[blockIdx.x]);
+    }
     // flush this (CTA, sequence) partial
     if (active) {
 #pragma unroll
@@ -862,7 +970,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       // the warp that arrives last for that pair merges the pair's slots.  No
       // CTA-wide meeting, so the other warps run straight into the next sequence.
       const int t0s = prefix[s], t1s = prefix[s + 1];
-      const int c0 = t0s / per, c1 = (t1s - 1) / per;
+      const int c0 = find_cta(bound, p.n_cta_x, t0s), c1 = find_cta(bound, p.n_cta_x, t1s - 1);
       const int slot_lo = (c0 + s) * WPH, slot_hi = (c1 + s) * WPH + WPH - 1;
       __threadfence();
       __syncwarp();
