@@ -287,6 +287,139 @@ def build_workload(name, context, N, rank, dev):
 
 
 # --------------------------------------------------------------------------- #
+# full decode step (BASELINE configuration 5): random-init Llama-3-8B architecture,
+# attention over the sharded KV, everything else on GPU 0
+# --------------------------------------------------------------------------- #
+def run_llama_step(args):
+    import torch
+    import torch.distributed as dist
+    from peerkv_b200 import _lib, ops
+    from peerkv_b200.decoder import DecodeStep, LlamaGeometry, ModelWeights, ShardedKVLayer, make_args
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    N = args.gpus
+    if world != N:
+        raise SystemExit(f"--gpus {N} but WORLD_SIZE={world}")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if N > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=dev)
+    g = LlamaGeometry(n_layers=args.layers)
+    ctx = args.context or 1048576
+    wl = build_workload("long-bf16", ctx, N, rank, dev)
+    B, HQ = wl["B"], wl["HQ"]
+    base, tab, lens = wl["pool"], wl["tab"], wl["len"]
+    append = None
+    if rank == 0:
+        # the new token of every sequence goes to one more page that GPU 0 owns
+        n0 = base.shape[1]
+        base = torch.cat([base, torch.zeros(2, B, PAGE, HKV, D, dtype=base.dtype, device=dev)], dim=1)
+        used = (lens.to(torch.int64) + PAGE - 1) // PAGE
+        tab = torch.cat([tab, torch.zeros(B, 1, dtype=torch.int32, device=dev)], dim=1)
+        tab[torch.arange(B, device=dev), used] = torch.arange(n0, n0 + B, device=dev, dtype=torch.int32)
+        full = (lens % PAGE) == 0
+        assert bool(full.all()), "the bench context puts whole pages on every GPU"
+        lens = lens + 1
+        append = (torch.arange(n0, n0 + B, device=dev), torch.zeros(B, dtype=torch.int64, device=dev))
+    layers = [ShardedKVLayer(base if li == 0 else base.clone(), tab, lens) for li in range(g.n_layers)]
+    qbuf = torch.zeros(B, HQ, D, dtype=torch.bfloat16, device=dev)
+    L = _lib.lib()
+    st = ops._stream(dev)
+    scale = 1.0 / math.sqrt(D)
+    largs = [make_args(qbuf, l, scale) for l in layers]
+    if N == 1:
+        shard = ops.Shard(dev, B, HQ)
+        grp = None
+
+        def attend(li, q, out):
+            qbuf.copy_(q)
+            _lib.check(L.pkv_decode(shard._h, C.byref(largs[li]), out.data_ptr(), _lib.PKV_BF16, None, st))
+    else:
+        from peerkv_b200.distributed import DistPeerGroup
+        grp = DistPeerGroup(dev, B, HQ, home=0)
+        shard = grp.shard
+
+        def attend(li, q, out):
+            qbuf.copy_(q)
+            grp.step(largs[li], q=qbuf, out=out)
+
+    weights = ModelWeights(g, dev) if rank == 0 else None
+    step = DecodeStep(g, weights, layers, attend, append)
+    if rank == 0 and not args.no_graphs:
+        step.capture(B)
+    tokens = torch.randint(0, g.vocab, (B,), device=dev)
+    positions = torch.full((B,), ctx, device=dev, dtype=torch.int64)
+    attn_out = torch.empty(B, HQ, D, dtype=torch.bfloat16, device=dev)
+
+    def one_token():
+        if rank == 0:
+            step.home_step(tokens, positions)
+        else:
+            for li in range(g.n_layers):
+                grp.step(largs[li])
+
+    def attention_only():
+        if rank == 0:
+            for li in range(g.n_layers):
+                attend(li, qbuf, attn_out)
+        else:
+            for li in range(g.n_layers):
+                grp.step(largs[li])
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if N > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if N > 1:
+            dist.barrier()
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t)
+        return ms / n
+
+    for _ in range(max(args.warmup, 3)):
+        one_token()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    tpot = timed(one_token, args.steps)
+    attn = timed(attention_only, args.steps)
+    clocks = sampler.stop() if sampler else None
+    status = shard.status() | (grp.xchg.status() if grp else 0)
+    if rank == 0:
+        peak, kind = measured_peak()
+        kv_bytes = wl["total_tokens"] * wl["bytes_per_token"] * g.n_layers
+        floor_ms = (kv_bytes / N + weights.bytes() - weights.embed.numel() * 2) / (peak * 1e9) * 1e3
+        print(json.dumps({
+            "metric": "tpot_ms", "value": tpot, "unit": "ms", "n_gpus": N, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": tpot, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"llama-step: random-init Llama-3-8B architecture ({g.n_layers} layers, hidden "
+                                   f"{g.hidden}, {g.n_q_heads}/{g.n_kv_heads} heads, FFN {g.ffn}, vocab {g.vocab}), "
+                                   f"batch {B}, {ctx}-token KV per sequence, pages round-robin over {N} GPU(s), "
+                                   "attention on the sharded path, the rest on GPU 0 with torch ops" + ("" if args.no_graphs else " replayed as CUDA graphs"),
+                       "kv_bytes_per_token_step": kv_bytes, "weight_bytes": weights.bytes()},
+            "attention_ms_per_token": attn, "attention_us_per_layer": attn / g.n_layers * 1e3,
+            "rest_ms_per_token": tpot - attn,
+            "hbm_floor_ms": floor_ms, "frac_of_floor": floor_ms / tpot, "peak_kind": kind,
+            "gpu_launches": args.steps * g.n_layers * (1 if N == 1 else N + 1),
+            "clocks": clocks, "device_status": status}), flush=True)
+    if grp:
+        grp.close()
+        dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------- #
 # our arm
 # --------------------------------------------------------------------------- #
 def main():
@@ -296,15 +429,19 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--workload", default="paged-bf16",
-                    choices=["paged-bf16", "ragged-bf16", "quant-int8", "quant-fp8", "long-bf16"],
+                    choices=["paged-bf16", "ragged-bf16", "quant-int8", "quant-fp8", "long-bf16", "llama-step"],
                     help="paged-bf16 is the headline configuration; the others are the remaining "
                          "BASELINE configurations' attention shapes")
     ap.add_argument("--context", type=int, default=0, help="tokens per sequence, 0 = the workload's own")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--lean", action="store_true", help="timed steps only (for runs under a profiler)")
+    ap.add_argument("--layers", type=int, default=32, help="llama-step only")
+    ap.add_argument("--no-graphs", action="store_true", help="llama-step only: eager torch ops around attention")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload == "llama-step":
+        return run_llama_step(args)
 
     import torch
     import torch.distributed as dist
