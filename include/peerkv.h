@@ -131,7 +131,7 @@ int pkv_decode(pkv_shard* s, const pkv_decode_args* a, void* out, int32_t out_dt
  * already fully handed out, a serving process that pre-sizes all GPU memory at start-up
  * and treats any later allocation as a fault, or code on a path where the allocator's
  * implicit device synchronisation is not acceptable.  For them the split-K scratch
- * lives in arrays that are part of the library image itself: about 14.8 MB per GPU, held
+ * lives in arrays that are part of the library image itself: about 16 MB per GPU, held
  * by every GPU that loads the library until the process ends.
  *
  * Same arguments and result as pkv_decode, minus the shard object.  Limits, checked

@@ -87,6 +87,8 @@ struct pkv_shard {
   int max_batch = 0;
   int n_q_heads = 0;
   int n_slots = 0;
+  int grp_slot0 = 0;
+  size_t grp_counter_off = 0;        // word offset of the group counters inside `counters`
   float* part_o = nullptr;
   float* part_ml = nullptr;
   uint32_t* status = nullptr;       // device word
@@ -323,6 +325,8 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   p.o_part = lo.o_part;
   p.lse_part = lo.lse_part;
   p.seq_counter = s->counters + 64;
+  p.grp_counter = s->counters + s->grp_counter_off;
+  p.grp_slot0 = s->grp_slot0;
   p.all_counter = s->counters;
   p.done_flag = lo.done_flag;
   p.done_epoch = lo.done_epoch;
@@ -436,7 +440,8 @@ int pkv_shard_create(pkv_shard** out, int device, int max_batch, int n_q_heads) 
   s->num_sms = sms;
   s->max_batch = max_batch;
   s->n_q_heads = n_q_heads;
-  s->n_slots = (sms + max_batch) * pkv::kMaxWph;
+  s->grp_slot0 = (sms + max_batch) * pkv::kMaxWph;                 // per-CTA slots, then per-group slots
+  s->n_slots = s->grp_slot0 + (sms + pkv::kGroupCtas - 1) / pkv::kGroupCtas + max_batch;
   s->maps.reserve(32);
   const size_t o_bytes = (size_t)s->n_slots * n_q_heads * pkv::kHeadDim * sizeof(float);
   const size_t ml_bytes = (size_t)s->n_slots * n_q_heads * 2 * sizeof(float);
@@ -444,7 +449,9 @@ int pkv_shard_create(pkv_shard** out, int device, int max_batch, int n_q_heads) 
   if (e == cudaSuccess) e = cudaMalloc(&s->part_ml, ml_bytes);
   if (e == cudaSuccess) e = cudaMalloc(&s->status, 256);
   if (e == cudaSuccess) e = cudaMemset(s->status, 0, 256);
-  s->n_counter_words = (size_t)n_q_heads * max_batch + 64;   // n_kv_heads <= n_q_heads
+  s->grp_counter_off = 64 + (size_t)n_q_heads * max_batch;
+  s->n_counter_words = s->grp_counter_off +
+                       (size_t)(pkv::kMaxCtas / pkv::kGroupCtas + max_batch) * n_q_heads;   // n_kv_heads <= n_q_heads
   const size_t obs_words = 1 + 3 * pkv::kMaxCtas;
   if (e == cudaSuccess) e = cudaMalloc(&s->counters, (s->n_counter_words + 2 * obs_words) * sizeof(unsigned int));
   if (e == cudaSuccess) e = cudaMemset(s->counters, 0, (s->n_counter_words + 2 * obs_words) * sizeof(unsigned int));
@@ -821,11 +828,14 @@ constexpr int kStaticMaxBatch = 32;
 constexpr int kStaticMaxQHeads = 64;
 constexpr int kStaticMaxSms = 192;
 constexpr int kStaticMaxDevices = 16;
-constexpr size_t kStaticSlots = (size_t)(kStaticMaxSms + kStaticMaxBatch) * pkv::kMaxWph;
+constexpr size_t kStaticGrpSlot0 = (size_t)(kStaticMaxSms + kStaticMaxBatch) * pkv::kMaxWph;
+constexpr size_t kStaticSlots = kStaticGrpSlot0 + kStaticMaxSms / pkv::kGroupCtas + 1 + kStaticMaxBatch;
 constexpr size_t kStaticObsWords = 1 + 3 * pkv::kMaxCtas;
-constexpr size_t kStaticWords = 128 + (size_t)kStaticMaxBatch * kStaticMaxQHeads;   // cleared per call
+constexpr size_t kStaticGrpOff = 64 + (size_t)kStaticMaxBatch * kStaticMaxQHeads;    // relative to the counters
+constexpr size_t kStaticWords = 64 + kStaticGrpOff +
+    (size_t)(pkv::kMaxCtas / pkv::kGroupCtas + kStaticMaxBatch) * kStaticMaxQHeads;   // cleared per call
 
-// One copy per GPU that loads the library, held until the process exits (14.8 MB).
+// One copy per GPU that loads the library, held until the process exits (16 MB).
 // In host code these names are only handles for cudaGetSymbolAddress, never pointers.
 static __device__ __align__(256) float g_static_part_o[kStaticSlots * kStaticMaxQHeads * pkv::kHeadDim];
 static __device__ __align__(256) float g_static_part_ml[kStaticSlots * kStaticMaxQHeads * 2];
@@ -865,6 +875,8 @@ int static_setup(int device) {
   s.done_counter = pw + 16;
   s.counters = pw + 64;                                // 64 global words, then per (sequence, kv-head)
   s.n_counter_words = kStaticWords - 64;
+  s.grp_counter_off = kStaticGrpOff;
+  s.grp_slot0 = static_cast<int>(kStaticGrpSlot0);
   s.obs[0] = pw + kStaticWords;           // survive from call to call (not cleared)
   s.obs[1] = s.obs[0] + kStaticObsWords;
   s.cache_maps = false;                                // tensor maps are encoded on the stack

@@ -40,6 +40,8 @@ constexpr int kMaxWph = 2;
 __host__ __device__ constexpr int cta_threads(int wph) { return (kHeadsPerCta * wph + kProducerWarps + 1) * 32; }
 constexpr int kMaxBatch = 4096;
 constexpr int kMaxCtas = 256;       // CTAs along x (one per SM)
+constexpr int kGroupCtas = 16;      // CTAs per first-level group of the two-level split-K merge
+constexpr int kGroupThreshold = 32; // slots per (sequence, kv-head) above which the merge is two-level
 
 constexpr uint32_t kPollLimit = 1u << 20;  // polls of mbarrier.try_wait before giving up
 
@@ -80,6 +82,8 @@ struct DecodeParams {
   float* o_part;               // [B][Hq][128] f32 normalised shard partial, or null (may be P2P)
   float* lse_part;             // [B][Hq] natural log, or null (may be P2P)
   unsigned int* seq_counter;   // [batch][n_kv_heads], zero between launches
+  unsigned int* grp_counter;   // [(CTA groups + batch)][n_kv_heads], zero between launches
+  int grp_slot0;               // first slot index of the per-group partials
   unsigned int* all_counter;   // sequences finished, zero between launches
   uint64_t* done_flag;         // released with done_epoch when every sequence is out (may be P2P)
   uint64_t done_epoch;
@@ -188,7 +192,7 @@ __device__ __forceinline__ void fold_slot(float& M, float& L, float4& acc, float
 // shuffle in between) and only then does the arithmetic.
 template <int NH, int NS>   // heads per pass, slots (or peer parts) loaded per round
 __device__ __forceinline__ void combine_heads(const DecodeParams& p, int b, int qh0, int nh,
-                                              int c0, int c1, int lane) {
+                                              int c0, int c1, int lane, int emit_slot = -1) {
   float4 acc[NH];
   float M[NH], L[NH];
 #pragma unroll
@@ -218,6 +222,18 @@ __device__ __forceinline__ void combine_heads(const DecodeParams& p, int b, int 
         for (int i = 0; i < NH; ++i) fold_slot(M[i], L[i], acc[i], ml[jj][i].x, ml[jj][i].y, os[jj][i]);
       }
     }
+  }
+  if (emit_slot >= 0) {
+    // first level of a two-level merge: the result stays an unnormalised slot
+#pragma unroll
+    for (int i = 0; i < NH; ++i) {
+      if (i < nh) {
+        const int64_t row = (int64_t)emit_slot * p.n_q_heads + qh0 + i;
+        *reinterpret_cast<float4*>(p.part_o + row * kHeadDim + lane * 4) = acc[i];
+        if (lane == 0) *reinterpret_cast<float2*>(p.part_ml + row * 2) = make_float2(M[i], L[i]);
+      }
+    }
+    return;
   }
   // The peers' shard partials are slots too: (m = lse * log2 e, l = 1, o = O normalised).
   for (int r0 = 0; r0 < p.mg_n; r0 += NS) {
@@ -262,11 +278,12 @@ __device__ __forceinline__ void combine_heads(const DecodeParams& p, int b, int 
 // one head per pass, eight slots per round (the 4x4 form would spill and serialise).
 template <bool LIGHT>
 __device__ __forceinline__ void combine_group(const DecodeParams& p, int b, int qh0, int nq,
-                                              int c0, int c1, int lane) {
+                                              int c0, int c1, int lane, int emit_slot = -1) {
   if constexpr (LIGHT) {
-    for (int i = 0; i < nq; ++i) combine_heads<1, 8>(p, b, qh0 + i, 1, c0, c1, lane);
+    for (int i = 0; i < nq; ++i) combine_heads<1, 8>(p, b, qh0 + i, 1, c0, c1, lane, emit_slot);
   } else {
-    for (int i = 0; i < nq; i += 4) combine_heads<4, 4>(p, b, qh0 + i, min(4, nq - i), c0, c1, lane);
+    for (int i = 0; i < nq; i += 4)
+      combine_heads<4, 4>(p, b, qh0 + i, min(4, nq - i), c0, c1, lane, emit_slot);
   }
 }
 
@@ -975,17 +992,52 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       __threadfence();
       __syncwarp();
       int last = 0;
-      if (lane == 0) {
-        unsigned int* ctr = p.seq_counter + (size_t)s * p.n_kv_heads + kvh;
-        const unsigned int prev = atomicAdd(ctr, 1u);
-        last = prev == (unsigned int)(slot_hi - slot_lo);
-        if (last) *ctr = 0;
-        __threadfence();
+      int lo = slot_lo, hi = slot_hi;          // what the final merge reads
+      if (slot_hi - slot_lo + 1 <= kGroupThreshold) {
+        if (lane == 0) {
+          unsigned int* ctr = p.seq_counter + (size_t)s * p.n_kv_heads + kvh;
+          const unsigned int prev = atomicAdd(ctr, 1u);
+          last = prev == (unsigned int)(slot_hi - slot_lo);
+          if (last) *ctr = 0;
+          __threadfence();
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+      } else {
+        // A sequence spread over many CTAs (small batches): merge in two levels so the
+        // last warp does not walk a hundred slots alone.  CTAs are grouped by
+        // c / kGroupCtas; the last warp of a group folds the group's slots into one
+        // group slot, then counts the group in; the last group folds the group slots.
+        const int gi = blockIdx.x / kGroupCtas, g_lo = c0 / kGroupCtas, g_hi = c1 / kGroupCtas;
+        const int cg0 = max(c0, gi * kGroupCtas), cg1 = min(c1, gi * kGroupCtas + kGroupCtas - 1);
+        int glast = 0;
+        if (lane == 0) {
+          unsigned int* ctr = p.grp_counter + (size_t)(gi + s) * p.n_kv_heads + kvh;
+          const unsigned int prev = atomicAdd(ctr, 1u);
+          glast = prev == (unsigned int)((cg1 - cg0 + 1) * WPH - 1);
+          if (glast) *ctr = 0;
+          __threadfence();
+        }
+        glast = __shfl_sync(0xffffffffu, glast, 0);
+        if (glast) {
+          combine_group<(WPH > 1)>(p, s, kvh * G, G, (cg0 + s) * WPH, (cg1 + s) * WPH + WPH - 1, lane,
+                                   p.grp_slot0 + gi + s);
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) {
+            unsigned int* ctr = p.seq_counter + (size_t)s * p.n_kv_heads + kvh;
+            const unsigned int prev = atomicAdd(ctr, 1u);
+            last = prev == (unsigned int)(g_hi - g_lo);
+            if (last) *ctr = 0;
+            __threadfence();
+          }
+          last = __shfl_sync(0xffffffffu, last, 0);
+          lo = p.grp_slot0 + g_lo + s;
+          hi = p.grp_slot0 + g_hi + s;
+        }
       }
-      last = __shfl_sync(0xffffffffu, last, 0);
       if (last && p.mg_n > 0) last = wait_peer_flags(p, lane) ? 1 : 0;   // home: peers' rows needed
       if (last) {
-        combine_group<(WPH > 1)>(p, s, kvh * G, G, slot_lo, slot_hi, lane);
+        combine_group<(WPH > 1)>(p, s, kvh * G, G, lo, hi, lane);
         if (p.done_flag) {
           __threadfence_system();
           __syncwarp();
