@@ -20,7 +20,9 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("PEERKV_REFERENCE", "/root/reference")
+HERE0 = os.path.dirname(os.path.abspath(__file__))
+REF = os.environ.get("PEERKV_REFERENCE",
+                     os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE0))), "reference"))
 sys.path.insert(0, REF)
 
 from umallm.peer_parallel_attn import (flash_partial, merge_partial,  # noqa: E402
