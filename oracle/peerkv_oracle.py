@@ -40,7 +40,7 @@ NOT in the reference, defined here once (parity unpinned for these):
 from __future__ import annotations
 
 import math
-from typing import List, Optional, Sequence, Tuple
+from typing import List, Sequence
 
 import numpy as np
 import torch

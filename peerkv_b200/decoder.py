@@ -14,7 +14,6 @@ home GPU owns ("newest page local"), so the append is a local write.
 """
 from __future__ import annotations
 
-import ctypes as C
 import math
 from dataclasses import dataclass
 from typing import List, Optional

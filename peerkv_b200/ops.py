@@ -83,8 +83,8 @@ def get_shard(device: torch.device, batch: int, n_q_heads: int) -> Shard:
         if s is not None:
             torch.cuda.synchronize(device)
             s.close()
-        cap = max(64, 1 << max(0, (batch - 1)).bit_length())
-        s = Shard(device, min(cap, 4096) if batch <= 4096 else batch, n_q_heads)
+        cap = min(4096, max(64, 1 << max(0, batch - 1).bit_length()))   # next power of two, 64..4096
+        s = Shard(device, max(cap, batch), n_q_heads)                    # > 4096: let the library refuse it
         _shards[key] = s
     return s
 

@@ -14,8 +14,6 @@ cast, and the N partials are merged in one pass instead of a left fold.
 """
 from __future__ import annotations
 
-import math
-
 try:
     import torch  # noqa: F401
     HAS_TORCH = True

@@ -19,7 +19,6 @@ from __future__ import annotations
 import logging
 import math
 import os
-from typing import Optional
 
 import torch
 

@@ -65,7 +65,6 @@ def main():
         dist.destroy_process_group()
         return
 
-    import ctypes as C  # noqa: F401
     import math
     local_rank = int(os.environ.get("LOCAL_RANK", rank))
     dev = torch.device("cuda", local_rank)

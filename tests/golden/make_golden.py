@@ -13,7 +13,6 @@ the outputs.  The tests never import the reference: they replay these vectors.
 """
 from __future__ import annotations
 
-import hashlib
 import os
 import sys
 

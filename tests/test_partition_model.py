@@ -2,7 +2,6 @@
 partial-slot numbering, arrival counts of the one- and two-level split-K merge), checked
 for the invariants the device code relies on.  Constants mirror
 peerkv_b200/csrc/decode_kernel.cuh; the scratch sizes mirror pkv_shard_create."""
-import math
 import random
 
 import pytest

@@ -1,8 +1,6 @@
 """Cost helpers, selector and do-no-harm rules of the compute-follows-KV path: the
 assertions of the reference's tests/test_peer_parallel_cost.py and the CFK-relevant
 rules of tests/test_no_harm.py, on the B200-calibrated model."""
-import math
-
 import pytest
 
 from peerkv_b200 import placement as pl

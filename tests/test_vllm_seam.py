@@ -7,7 +7,6 @@ import pytest
 import torch
 
 from golden_cases import gen_paged_case
-from oracle import peerkv_oracle as orc
 
 
 def _impl():
