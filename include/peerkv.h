@@ -60,7 +60,9 @@ typedef struct pkv_exchange pkv_exchange; /* one GPU's mailboxes for q and parti
  * T tokens: page_size = T, token_stride = D, head_stride = T*D.
  * Strides must be multiples of 8 elements (16 bytes for 1-byte codes), bases
  * 16-byte aligned, head_dim 128.  k_scale / v_scale ([page][tok][head] fp16,
- * dense) are NULL unless dtype is PKV_INT8 or PKV_FP8_E4M3. */
+ * dense) are NULL unless dtype is PKV_INT8 or PKV_FP8_E4M3; quantised pools also need
+ * page_size to be a multiple of 16 and n_kv_heads <= 8 or a multiple of 8.  At most 8
+ * query heads per kv head. */
 typedef struct pkv_kv_view {
   const void* k;
   const void* v;
@@ -103,7 +105,10 @@ int pkv_abi_version(void);
 /* ---- one GPU ------------------------------------------------------------ */
 
 /* Allocates the split-K scratch of one GPU once (no allocation per call; the
- * reference allocates 6-14 tensors per call, csrc/peer_fused_attn_ext.cu:56-92). */
+ * reference allocates 6-14 tensors per call, csrc/peer_fused_attn_ext.cu:56-92).
+ * A shard is used from one host thread, and its launches must not overlap on the GPU
+ * (one stream, or ordered streams): they share the scratch, and each launch records
+ * per-SM timings that the next one uses to split the work. */
 int pkv_shard_create(pkv_shard** out, int device, int max_batch, int n_q_heads);
 int pkv_shard_destroy(pkv_shard* s);
 /* Reads (and clears) the device status word; synchronises `stream` first. */
