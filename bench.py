@@ -1,19 +1,22 @@
 """Benchmark of peer-parallel split-K decode attention on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Workload (BASELINE configuration "batched paged decode attention"): batch 16,
-32 query / 8 kv heads, head_dim 128, 131072-token context per sequence, bf16 KV in
-16-token pages, block table = seeded random permutation of the page pool; for
-N > 1 page p lives on GPU p mod N (strong scaling: the same 8 GiB of KV is split),
-q is resident on GPU 0 and the partials are merged on GPU 0.  A step is one
-decode-attention layer.  Synthetic N(0,1) data.
+Headline workload `paged-bf16` (batched paged decode attention): batch 16, 32 query / 8
+kv heads, head_dim 128, 131072-token context per sequence, bf16 KV in 16-token pages,
+block table = seeded random permutation of the page pool; for N > 1 page p lives on GPU
+p mod N (strong scaling: the same 8 GiB of KV is split), q is resident on GPU 0 and the
+partials are merged on GPU 0.  A step is one decode-attention layer.  Synthetic N(0,1)
+data stands in for everything (the path has no dataset).
 
-Prints ONE JSON line: effective KV GB/s (algorithmic KV bytes / step time) with
-the per-layer latency, the roofline of the dominant kernel, an end-to-end number
-with host buffers, and the CPU baseline (the oracle port of the reference's torch
-path, timed on this box's host cores).
+Prints ONE JSON line: effective KV GB/s (algorithmic KV bytes / step time) with the
+per-layer latency, the roofline of the dominant kernel, an end-to-end number with host
+buffers, a parity check of the timed output against the CPU oracle at full context
+(every rank checks its own shard, partials are gathered and merged on rank 0; the run
+exits non-zero when it fails), the same for the other attention shapes (`workloads`,
+a few steps each), and the CPU baseline: the reference's torch path timed on this box's
+host cores on a bounded sample.
 """
 from __future__ import annotations
 
@@ -30,13 +33,23 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-B, HQ, HKV, D, PAGE = 16, 32, 8, 128, 16
-CTX = 131072
-BYTES_PER_TOKEN = 2 * HKV * D * 2            # K and V, bf16
+D, PAGE = 128, 16
 PEAK_FALLBACK_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of decode_partial_kernel per launch,
-# measured with ncu on a 1 GiB pool and scaled by tokens (profiles/decode_partial_bf16_paged.md)
-NCU_TRAFFIC_PER_ALGO_BYTE = (1.07455e9 + 4.46e6) / 1073741824
+# dram__bytes_read.sum + dram__bytes_write.sum of decode_partial_kernel per launch and
+# algorithmic byte, from ncu captures on 1 GiB pools (traffic grows in proportion to the
+# tokens read)
+NCU_TRAFFIC_PER_ALGO_BYTE = {"bf16": (1.07455e9 + 4.46e6) / 1073741824, "int8": 1.002, "fp8": 1.002}
+METRIC = "decode_attn_effective_kv_bandwidth"
+
+WORKLOADS = {
+    # name: batch, Hq, Hkv, tokens per sequence (None = ragged), kv format, placement
+    "paged-bf16": dict(B=16, HQ=32, HKV=8, ctx=131072, fmt="bf16", place="round_robin"),
+    "ragged-bf16": dict(B=64, HQ=32, HKV=8, ctx=None, fmt="bf16", place="capacity_spill"),
+    "quant-int8": dict(B=8, HQ=64, HKV=8, ctx=524288, fmt="int8", place="round_robin"),
+    "quant-fp8": dict(B=8, HQ=64, HKV=8, ctx=524288, fmt="fp8", place="round_robin"),
+    "long-bf16": dict(B=4, HQ=32, HKV=8, ctx=1048576, fmt="bf16", place="round_robin"),
+}
+EXTRA_WORKLOADS = ["long-bf16", "ragged-bf16", "quant-int8", "quant-fp8"]
 
 
 def measured_peak():
@@ -45,6 +58,38 @@ def measured_peak():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return PEAK_FALLBACK_GBS, "fallback"
+
+
+def bytes_per_token(w):
+    return 2 * w["HKV"] * D * 2 if w["fmt"] == "bf16" else 2 * w["HKV"] * D + 2 * w["HKV"] * 2
+
+
+def workload_lengths(name, context):
+    import numpy as np
+    w = WORKLOADS[name]
+    rng = np.random.default_rng(1234)
+    if w["ctx"] is None:
+        lens = rng.integers(4096, 262144 + 1, size=w["B"]).astype(np.int64)
+        if context:
+            lens = np.maximum(1, lens * context // 262144)
+    else:
+        lens = np.full(w["B"], context or w["ctx"], dtype=np.int64)
+    return lens, rng
+
+
+def workload_config(name, n, context=0):
+    """The one description of a workload that both arms print."""
+    w = WORKLOADS[name]
+    lens, _ = workload_lengths(name, context)
+    ctx_desc = "ragged U[4096, 262144]" if w["ctx"] is None else str(int(lens[0]))
+    if w["ctx"] is None and context:
+        ctx_desc += f" scaled by {context}/262144"
+    return {"workload": f"{name}: batch {w['B']}, Hq {w['HQ']}, Hkv {w['HKV']}, head_dim {D}, context "
+                        f"{ctx_desc}/seq, {w['fmt']} KV, {PAGE}-token pages, random-permutation block table",
+            "batch": w["B"], "context": ctx_desc, "page_size": PAGE,
+            "kv_bytes_per_layer": int(lens.sum()) * bytes_per_token(w),
+            "sharding": f"{w['place']} pages over {n} GPU(s), q and merge on GPU 0",
+            "l2_policy": "inputs larger than L2 (KV per GPU >= 1 GiB, read once per step)"}
 
 
 class ClockSampler:
@@ -109,32 +154,64 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- #
-# reference arm / cpu baseline: the oracle port on host cores
+# reference arm / cpu baseline: the reference's own torch path on host cores
 # --------------------------------------------------------------------------- #
-def cpu_sample_inputs(tokens: int, seed: int = 0):
+def load_reference():
+    """The reference's Python implementation of the path, when `make -C oracle` placed it
+    under oracle/_ref (kind "reference"); else the oracle's restatement (kind "port").
+    Returns (gather_seq, peer_parallel_attention, kind)."""
+    ref_root = os.path.join(ROOT, "oracle", "_ref", "ref_py")
+    if os.path.exists(os.path.join(ref_root, "umallm", "peer_parallel_attn.py")):
+        if ref_root not in sys.path:
+            sys.path.insert(0, ref_root)
+        try:
+            from umallm.peer_parallel_attn import peer_parallel_attention
+            from umallm.peerkv.paged import gather_seq
+            return gather_seq, peer_parallel_attention, "reference"
+        except Exception:      # an incomplete copy: fall through to the port
+            pass
+    from oracle import peerkv_oracle as orc
+
+    def gather_seq(local_cache, peer_cache, block_row, seq_len, peer_base):
+        n_blk = (seq_len + PAGE - 1) // PAGE
+        ids, val = orc.split_block_row(block_row[:n_blk].tolist(), seq_len, PAGE,
+                                       [0] if peer_cache is None else [0, peer_base])
+        Kl, Vl = orc.cat_blocks(local_cache, ids[0], val[0])
+        if peer_cache is None or val[1] == 0:
+            return Kl, Vl, None, None
+        Kp, Vp = orc.cat_blocks(peer_cache, ids[1], val[1])
+        return Kl, Vl, Kp, Vp
+    return gather_seq, orc.peer_parallel_attention, "port"
+
+
+def cpu_sample_inputs(name, tokens: int, n_shards: int, seed: int = 0):
+    """One sequence of the workload at `tokens` tokens: paged pool(s) and a permuted block
+    table.  With two or more shards the pages are split in the reference's own form: ids
+    below peer_base in a local cache, the rest in a peer cache."""
     import torch
+    w = WORKLOADS[name]
     g = torch.Generator().manual_seed(seed)
     n_pages = tokens // PAGE
-    pool = torch.randn(2, n_pages, PAGE, HKV, D, generator=g).bfloat16()
-    bt = torch.randperm(n_pages, generator=g).to(torch.int32).view(1, -1)
-    q = torch.randn(1, HQ, D, generator=g).bfloat16()
-    return q, pool, bt, torch.tensor([tokens], dtype=torch.int32)
+    pool = torch.randn(2, n_pages, PAGE, w["HKV"], D, generator=g).bfloat16()
+    bt = torch.randperm(n_pages, generator=g).to(torch.int32)
+    q = torch.randn(1, w["HQ"], 1, D, generator=g).bfloat16()
+    if n_shards > 1:
+        base = n_pages // 2
+        return q, pool[:, :base].contiguous(), pool[:, base:].contiguous(), bt, tokens, base
+    return q, pool, None, bt, tokens, 1 << 62
 
 
-def cpu_reference_step(inputs, n_shards: int):
-    """The reference's path on CPU: per-sequence paged gather (peerkv/paged.py), one
-    partial per shard with GQA expansion and fp32 math, then the merge fold."""
-    from oracle import peerkv_oracle as orc
-    q, pool, bt, sl = inputs
-    tokens = int(sl[0])
-    n_pages = tokens // PAGE
-    per = n_pages // n_shards
-    shards = []
-    for s in range(n_shards):
-        ids = bt[0, s * per:(s + 1) * per].tolist() if s < n_shards - 1 else bt[0, s * per:].tolist()
-        K, V = orc.cat_blocks(pool, ids, len(ids) * PAGE)
-        shards.append((K.unsqueeze(0), V.unsqueeze(0)))
-    return orc.peer_parallel_attention(q.view(1, HQ, 1, D), shards)
+def cpu_reference_step(fns, inputs):
+    """The reference's path on CPU for one sequence: paged gather into contiguous shards
+    (umallm/peerkv/paged.py gather_seq), one partial per shard with GQA expansion and
+    fp32 math, then the merge fold (umallm/peer_parallel_attn.py peer_parallel_attention)."""
+    gather_seq, ppa, _ = fns
+    q, local, peer, bt, tokens, base = inputs
+    Kl, Vl, Kp, Vp = gather_seq(local, peer, bt, tokens, base)
+    shards = [(Kl.unsqueeze(0), Vl.unsqueeze(0))]
+    if Kp is not None:
+        shards.append((Kp.unsqueeze(0), Vp.unsqueeze(0)))
+    return ppa(q, shards)
 
 
 def run_reference(args):
@@ -142,71 +219,53 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    name = args.workload if args.workload in WORKLOADS else "paged-bf16"
+    w = WORKLOADS[name]
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
+    fns = load_reference()
     tokens = 32768
-    inputs = cpu_sample_inputs(tokens)
-    n_shards = max(1, args.gpus)
+    n_shards = 1 if args.gpus == 1 else 2
+    inputs = cpu_sample_inputs(name, tokens, n_shards)
     for _ in range(args.warmup):
-        cpu_reference_step(inputs, n_shards)
+        cpu_reference_step(fns, inputs)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_reference_step(inputs, n_shards)
+        cpu_reference_step(fns, inputs)
     dt = (time.perf_counter() - t0) / args.steps
-    gbs = tokens * BYTES_PER_TOKEN / dt / 1e9
-    sample = f"1 sequence x {tokens} tokens of the workload per step, {n_shards} shard(s), paged gather + fp32 math + merge"
+    gbs = tokens * 2 * w["HKV"] * D * 2 / dt / 1e9
+    sample = (f"1 sequence x {tokens} tokens of the workload per step (bf16 pool), {n_shards} shard(s) in the "
+              f"reference's local/peer form, paged gather + GQA expansion + fp32 math + merge; the rate is "
+              f"extrapolated to the whole workload linearly in tokens")
     line = {
-        "impl": "reference", "metric": "decode_attn_effective_kv_bandwidth", "value": gbs, "unit": "GB/s",
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic",
-        "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "data": "synthetic", "extrapolated": True,
+        "config": workload_config(name, args.gpus, args.context),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": fns[2], "sample": sample,
+                         "sample_tokens": tokens, "extrapolated": True},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n):
-    return {"workload": "batched paged decode attention: batch 16, Hq 32, Hkv 8, head_dim 128, "
-                        "context 131072/seq, bf16, 16-token pages, random-permutation block table",
-            "batch": B, "context": CTX, "page_size": PAGE, "kv_bytes_per_layer": B * CTX * BYTES_PER_TOKEN,
-            "sharding": f"round-robin pages over {n} GPU(s), q and merge on GPU 0",
-            "l2_policy": "inputs larger than L2 (KV per GPU >= 1 GiB, read once per step)"}
-
-
 # --------------------------------------------------------------------------- #
 # workloads (synthetic stand-ins with the shapes, sizes and value distributions of the
-# BASELINE configurations; N(0,1) KV, seeded)
+# benchmark configurations; N(0,1) KV, seeded)
 # --------------------------------------------------------------------------- #
-WORKLOADS = {
-    # name: batch, Hq, Hkv, tokens per sequence (None = ragged), kv format, placement
-    "paged-bf16": dict(B=16, HQ=32, HKV=8, ctx=131072, fmt="bf16", place="round_robin"),
-    "ragged-bf16": dict(B=64, HQ=32, HKV=8, ctx=None, fmt="bf16", place="capacity_spill"),
-    "quant-int8": dict(B=8, HQ=64, HKV=8, ctx=524288, fmt="int8", place="round_robin"),
-    "quant-fp8": dict(B=8, HQ=64, HKV=8, ctx=524288, fmt="fp8", place="round_robin"),
-    "long-bf16": dict(B=4, HQ=32, HKV=8, ctx=1048576, fmt="bf16", place="round_robin"),
-}
-
-
 def build_workload(name, context, N, rank, dev):
     """This rank's pool, local block table and shard lengths.  The global block table
     is the same seeded permutation on every rank; placement decides which pages are
-    this rank's (round robin: page p -> GPU p mod N at index p div N; capacity spill:
-    GPUs are filled in order up to a seeded fraction in [0.5, 1.0] of an equal share,
-    the rest spills to the next GPU)."""
+    this rank's (round robin: page p -> GPU p mod N at index p div N, split on the device
+    by the library; capacity spill: GPUs are filled in order up to a seeded fraction in
+    [0.5, 1.0] of an equal share, the rest spills to the next GPU)."""
     import numpy as np
     import torch
-    from peerkv_b200 import _lib, ops
+    from peerkv_b200 import _lib, ops, placement
     w = WORKLOADS[name]
     B, HQ, HKV = w["B"], w["HQ"], w["HKV"]
-    rng = np.random.default_rng(1234)
-    if w["ctx"] is None:
-        lens = rng.integers(4096, 262144 + 1, size=B).astype(np.int64)
-        if context:
-            lens = np.maximum(1, lens * context // 262144)
-    else:
-        lens = np.full(B, context or w["ctx"], dtype=np.int64)
+    lens, rng = workload_lengths(name, context)
     n_pages = (lens + PAGE - 1) // PAGE
     total_pages = int(n_pages.sum())
     W = int(n_pages.max())
@@ -217,6 +276,7 @@ def build_workload(name, context, N, rank, dev):
         bt[i, :n_pages[i]] = perm[k:k + n_pages[i]]
         k += int(n_pages[i])
     sl = lens.astype(np.int32)
+    caps = None
 
     if w["place"] == "round_robin":
         btd, sld = torch.from_numpy(bt).to(dev), torch.from_numpy(sl).to(dev)
@@ -229,28 +289,14 @@ def build_workload(name, context, N, rank, dev):
         torch.cuda.synchronize()
         my_tab, my_len = tabs[rank], lns[rank]
         n_local = (total_pages + N - 1) // N
-        rank_tokens = [int(x.sum()) for x in lns]
+        all_tokens = torch.stack(lns).cpu().numpy().astype(np.int64)          # [N, B]
     else:
         caps = np.random.default_rng(99).uniform(0.5, 1.0, size=N)
-        quota = [int(c * total_pages / N) for c in caps]
-        quota[-1] = total_pages
-        tab = np.zeros((N, B, W), dtype=np.int32)
-        cnt = np.zeros((N, B), dtype=np.int64)
-        tok = np.zeros((N, B), dtype=np.int64)
-        used = np.zeros(N, dtype=np.int64)
-        g = 0
-        for i in range(B):
-            for j in range(int(n_pages[i])):
-                while g < N - 1 and used[g] >= quota[g]:
-                    g += 1
-                tab[g, i, cnt[g, i]] = used[g]                # pools are compact: local id = arrival order
-                cnt[g, i] += 1
-                used[g] += 1
-                tok[g, i] += PAGE if j < n_pages[i] - 1 else lens[i] - (n_pages[i] - 1) * PAGE
+        tab, tok, used = placement.capacity_spill_split(n_pages, lens, PAGE, caps)
         my_tab = torch.from_numpy(tab[rank]).to(dev)
         my_len = torch.from_numpy(tok[rank].astype(np.int32)).to(dev)
         n_local = max(1, int(used[rank]))
-        rank_tokens = [int(tok[r].sum()) for r in range(N)]
+        all_tokens = tok
 
     torch.manual_seed(100 + rank)
     fmt = w["fmt"]
@@ -260,7 +306,6 @@ def build_workload(name, context, N, rank, dev):
         chunk = max(1, n_local // 8)
         for i in range(0, n_local, chunk):
             pool[:, i:i + chunk].normal_()
-        bpt = 2 * HKV * D * 2
     else:
         code_dt = torch.int8 if fmt == "int8" else torch.float8_e4m3fn
         pool = torch.empty(2, n_local, PAGE, HKV, D, dtype=code_dt, device=dev)
@@ -272,18 +317,103 @@ def build_workload(name, context, N, rank, dev):
             pool[:, i:i + chunk] = c
             sc[:, i:i + chunk] = s_
         scales = (sc[0], sc[1])
-        bpt = 2 * HKV * D + 2 * HKV * 2
-    ctx_desc = "ragged U[4096, 262144]" if w["ctx"] is None else str(int(lens[0]))
-    cfg = {"workload": f"{name}: batch {B}, Hq {HQ}, Hkv {HKV}, head_dim {D}, context {ctx_desc}/seq, "
-                       f"{fmt} KV, {PAGE}-token pages, random-permutation block table",
-           "batch": B, "context": ctx_desc, "page_size": PAGE,
-           "sharding": f"{w['place']} pages over {N} GPU(s), q and merge on GPU 0",
-           "l2_policy": "inputs larger than L2 (KV per GPU >= 1 GiB, read once per step)"}
-    return dict(B=B, HQ=HQ, HKV=HKV, pool=pool, scales=scales, tab=my_tab, len=my_len,
-                bytes_per_token=bpt, total_tokens=int(lens.sum()), max_rank_tokens=max(rank_tokens),
-                rank_tokens=rank_tokens,
+    return dict(name=name, B=B, HQ=HQ, HKV=HKV, fmt=fmt, pool=pool, scales=scales, tab=my_tab, len=my_len,
+                bytes_per_token=bytes_per_token(w), total_tokens=int(lens.sum()),
+                rank_tokens=[int(x) for x in all_tokens.sum(1)], all_tokens=all_tokens,
+                lens=lens, n_pages=n_pages, global_bt=bt, caps=caps,
                 q_dtype=torch.bfloat16, dtype="bf16" if fmt == "bf16" else "f16",
-                config=cfg)
+                config=workload_config(name, N, context))
+
+
+# --------------------------------------------------------------------------- #
+# parity of the timed output against the CPU oracle, at the workload's full context
+# --------------------------------------------------------------------------- #
+def oracle_shard_partial(wl, q_cpu, seq, chunk_tokens):
+    """CPU oracle partial (O fp32 [Hq, D], lse fp32 [Hq]) of this rank's shard for one
+    sequence.  The shard's pages of the sequence are fetched from the GPU in chunks; each
+    chunk is one call of the oracle's paged partial, and the chunks are merged with the
+    oracle's N-way merge (exactly what the path itself does across shards)."""
+    import torch
+    from oracle import peerkv_oracle as orc
+    L = int(wl["len"][seq])
+    Hq = wl["HQ"]
+    if L == 0:
+        return torch.zeros(Hq, D), torch.full((Hq,), float("-inf"))
+    n_blk = (L + PAGE - 1) // PAGE
+    ids = wl["tab"][seq, :n_blk].long()
+    pool, scales = wl["pool"], wl["scales"]
+    Os, Ls = [], []
+    per = max(1, chunk_tokens // PAGE)
+    for c0 in range(0, n_blk, per):
+        c1 = min(n_blk, c0 + per)
+        idc = ids[c0:c1]
+        toks = min(L, c1 * PAGE) - c0 * PAGE
+        raw = pool.view(torch.uint8) if pool.dtype == torch.float8_e4m3fn else pool
+        cache = raw.index_select(1, idc).cpu()
+        ks = vs = None
+        if scales is not None:
+            ks, vs = scales[0].index_select(0, idc).cpu(), scales[1].index_select(0, idc).cpu()
+        bt = torch.arange(c1 - c0, dtype=torch.int32).view(1, -1)
+        o, l = orc.paged_partial_oracle(q_cpu[seq:seq + 1], cache, bt, torch.tensor([toks]), None, ks, vs)
+        Os.append(o[0]); Ls.append(l[0])
+    if len(Os) == 1:
+        return Os[0], Ls[0]
+    return orc.merge_n(Os, Ls)
+
+
+def check_placement(wl, N, seqs):
+    """The placement this run used against the oracle's definition of it."""
+    import numpy as np
+    from oracle import peerkv_oracle as orc
+    if wl["caps"] is None:
+        rows = [wl["global_bt"][s] for s in seqs]
+        ref = orc.round_robin_shards(rows, [int(wl["lens"][s]) for s in seqs], PAGE, N)
+        return all(np.array_equal(ref[g][1].numpy().astype(np.int64), wl["all_tokens"][g][seqs]) for g in range(N))
+    # capacity spill over the whole batch (the oracle walks every page once)
+    bt = [wl["global_bt"][i, :int(wl["n_pages"][i])] for i in range(wl["B"])]
+    ref = orc.capacity_spill_shards(bt, [int(x) for x in wl["lens"]], PAGE, list(wl["caps"]))
+    return all(np.array_equal(ref[g][1].numpy().astype(np.int64), wl["all_tokens"][g]) for g in range(N))
+
+
+def parity_check(wl, q, out, N, rank, dev, n_seqs=2):
+    """Every rank: oracle partial of its own shard for the sampled sequences; rank 0 merges
+    the gathered partials with the oracle's merge and compares with the timed output at
+    |diff| <= 2e-3 + 1e-2 |ref|."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from oracle import peerkv_oracle as orc
+    lens = wl["lens"]
+    seqs = sorted({int(np.argmax(lens)), int(np.argmin(lens))} if wl["caps"] is not None else {0, wl["B"] - 1})
+    seqs = seqs[:n_seqs]
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(max(1, cores // N))
+    t0 = time.perf_counter()
+    q_cpu = q.cpu()
+    chunk = 65536 if wl["HQ"] <= 32 else 32768
+    parts = [oracle_shard_partial(wl, q_cpu, s, chunk) for s in seqs]
+    O = torch.stack([p[0] for p in parts]).to(dev)
+    Lse = torch.stack([p[1] for p in parts]).to(dev)
+    if N > 1:
+        Og = [torch.empty_like(O) for _ in range(N)]
+        Lg = [torch.empty_like(Lse) for _ in range(N)]
+        dist.all_gather(Og, O)
+        dist.all_gather(Lg, Lse)
+    else:
+        Og, Lg = [O], [Lse]
+    res = None
+    if rank == 0:
+        ref, _ = orc.merge_n([o.cpu() for o in Og], [l.cpu() for l in Lg])
+        got = out[seqs].float().cpu()
+        diff = (got - ref).abs()
+        ok = bool(torch.allclose(got, ref, atol=2e-3, rtol=1e-2))
+        res = {"checked": True, "against": "CPU oracle, per-rank shard partials at full context merged on rank 0",
+               "seqs": seqs, "seq_tokens": [int(lens[s]) for s in seqs], "tolerance": "abs 2e-3 + rel 1e-2",
+               "max_abs_err": float(diff.max()), "max_abs_ref": float(ref.abs().max()),
+               "placement_matches_oracle": bool(check_placement(wl, N, seqs)),
+               "oracle_seconds": round(time.perf_counter() - t0, 2), "ok": ok}
+        res["ok"] = bool(res["ok"] and res["placement_matches_oracle"])
+    return res
 
 
 # --------------------------------------------------------------------------- #
@@ -307,6 +437,7 @@ def run_llama_step(args):
     if N > 1:
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
+    HKV = WORKLOADS["long-bf16"]["HKV"]
     g = LlamaGeometry(n_layers=args.layers)
     ctx = args.context or 1048576
     wl = build_workload("long-bf16", ctx, N, rank, dev)
@@ -442,6 +573,7 @@ def run_single_layer(args):
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
     Bq, H, HK, T = 1, 32, 8, args.context or 16384
+    BYTES_PER_TOKEN = 2 * HK * D * 2
     n_sh = max(2, N)
     g = torch.Generator().manual_seed(0)
     q = torch.randn(Bq, H, 1, D, generator=g).half()
@@ -571,81 +703,54 @@ def run_single_layer(args):
 # --------------------------------------------------------------------------- #
 # our arm
 # --------------------------------------------------------------------------- #
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workload", default="paged-bf16",
-                    choices=["paged-bf16", "ragged-bf16", "quant-int8", "quant-fp8", "long-bf16", "llama-step", "single-fp16"],
-                    help="paged-bf16 is the headline configuration; the others are the remaining "
-                         "BASELINE configurations' attention shapes")
-    ap.add_argument("--context", type=int, default=0, help="tokens per sequence, 0 = the workload's own")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--lean", action="store_true", help="timed steps only (for runs under a profiler)")
-    ap.add_argument("--layers", type=int, default=32, help="llama-step only")
-    ap.add_argument("--no-graphs", action="store_true", help="llama-step only: eager torch ops around attention")
-    args = ap.parse_args()
-    if args.impl == "reference":
-        return run_reference(args)
-    if args.workload == "llama-step":
-        return run_llama_step(args)
-    if args.workload == "single-fp16":
-        return run_single_layer(args)
-
+def measure_workload(name, args, N, rank, local_rank, dev, steps, headline):
+    """Builds one workload on this rank, times `steps` steps (CUDA events between barriers,
+    max over ranks), times the shard kernel alone on every rank, checks the timed output
+    against the CPU oracle and, for the headline, measures the end-to-end step with host
+    buffers.  Returns the result dict on rank 0 (None elsewhere)."""
     import torch
     import torch.distributed as dist
     from peerkv_b200 import _lib, ops
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    N = args.gpus
-    if world != N:
-        raise SystemExit(f"--gpus {N} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {N}")
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    if N > 1:
-        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        dist.init_process_group("nccl", device_id=dev)
-    wl = build_workload(args.workload, args.context, N, rank, dev)
-    B, HQ, HKV = wl["B"], wl["HQ"], wl["HKV"]
+    wl = build_workload(name, args.context, N, rank, dev)
+    B, HQ = wl["B"], wl["HQ"]
     pool, my_tab, my_len = wl["pool"], wl["tab"], wl["len"]
     local_tokens = int(my_len.sum())
-    bytes_per_token = wl["bytes_per_token"]
+    bpt = wl["bytes_per_token"]
     qdt = wl["q_dtype"]
 
     torch.manual_seed(7)
     q_host = torch.randn(B, HQ, D).to(qdt).pin_memory()
     q = q_host.to(dev)
-    out = torch.empty(B, HQ, D, dtype=qdt, device=dev)
+    out = torch.zeros(B, HQ, D, dtype=qdt, device=dev)
     out_host = torch.empty(B, HQ, D, dtype=qdt).pin_memory()
-    tab_host = my_tab.cpu().pin_memory()
     len_host = my_len.cpu().pin_memory()
+    # the page a decode step may have to add per sequence: the last one of each row
+    used = ((my_len.to(torch.int64) + PAGE - 1) // PAGE - 1).clamp_(min=0)
+    new_page_host = my_tab.gather(1, used.view(-1, 1)).view(-1).cpu().pin_memory()
+    new_page_dev = torch.empty(B, dtype=torch.int32, device=dev)
+    rows = torch.arange(B, device=dev)
     scale = 1.0 / math.sqrt(D)
     view = ops.paged_view(pool[0], pool[1], *(wl["scales"] or (None, None)))
     out_code = ops._DT[qdt]
     L = _lib.lib()
     st = ops._stream(dev)
+    a = ops.make_args(q, view, my_tab, my_tab.stride(0), my_len, scale)
 
     if N == 1:
         shard = ops.Shard(dev, B, HQ)
-        a = ops.make_args(q, view, my_tab, my_tab.stride(0), my_len, scale)
+        grp = None
 
         def step():
             _lib.check(L.pkv_decode(shard._h, C.byref(a), out.data_ptr(), out_code, None, st))
-        launches_per_step = 1
-        grp = None
     else:
         from peerkv_b200.distributed import DistPeerGroup
         grp = DistPeerGroup(dev, B, HQ, home=0)
         shard = grp.shard
-        a = ops.make_args(q, view, my_tab, my_tab.stride(0), my_len, scale)
 
         def step():
             grp.step(a, q=q, out=out)
-        launches_per_step = N + 1      # one kernel per GPU per step, plus the q publish on GPU 0
+    launches_per_step = N          # one kernel per GPU per step (the home kernel also publishes q and merges)
 
     def barrier():
         if N > 1:
@@ -672,104 +777,266 @@ def main():
             ms = max(float(x) for x in allt)
         return ms
 
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    for _ in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 3)
+    sampler = ClockSampler(local_rank) if (rank == 0 and headline) else None
+    for _ in range(warm):
         step()
     barrier()
     if sampler:
         sampler.start()
-    total_ms = timed(step, args.steps)
-    ms_per_step = total_ms / args.steps
+    total_ms = timed(step, steps)
+    ms_per_step = total_ms / steps
     step_rank_ms = list(rank_ms)
     # keep the GPU under the same load long enough for the clock sampler to see it
     soak_steps = 0
-    if total_ms < 1500.0 and not args.lean:
+    if headline and total_ms < 1500.0 and not args.lean:
         soak_steps = int(min(20000, (1500.0 - total_ms) / max(ms_per_step, 1e-3))) + 1
         timed(step, soak_steps)
     clocks = sampler.stop() if sampler else None
     status = shard.status() | (grp.xchg.status() if grp else 0)
 
-    algo_bytes = wl["total_tokens"] * bytes_per_token
+    algo_bytes = wl["total_tokens"] * bpt
     value = algo_bytes / (ms_per_step * 1e-3) / 1e9
 
-    # ---- end to end: host buffers in, host result out, every step ------------- #
-    def e2e_step():
-        if rank == 0:
-            q.copy_(q_host, non_blocking=True)
-        my_tab.copy_(tab_host, non_blocking=True)
-        my_len.copy_(len_host, non_blocking=True)
-        step()
-        if rank == 0:
-            out_host.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-    for _ in range(3):
-        e2e_step()
-    e2e_n = 3 if args.lean else max(5, min(args.steps, 100))
-    e2e_ms = timed(e2e_step, e2e_n) / e2e_n
-    h2d = q_host.numel() * 2 + N * (tab_host.numel() * 4 + len_host.numel() * 4)
-    d2h = out_host.numel() * 2
+    # ---- optional: where the microseconds of a step go (device time stamps) ----------- #
+    timeline = None
+    if args.timeline:
+        timeline = step_timeline(L, shard, step, barrier, dev, N, rank)
 
-    # ---- dominant kernel alone (rank 0's shard), CUDA events around each launch ---- #
-    kern_ms = None
-    if rank == 0:
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-               for _ in range(2 if args.lean else 20)]
+    # ---- parity: the output of the last timed step against the CPU oracle ------------ #
+    parity = None
+    if not args.lean:
+        parity = parity_check(wl, q, out, N, rank, dev)
+
+    # ---- end to end: host buffers in, host result out, every step ------------------- #
+    e2e = None
+    if headline:
+        def e2e_step():
+            # what a decode step changes: the query, every sequence's length on the GPU that
+            # took the new token, and at most one new page id per sequence
+            if rank == 0:
+                q.copy_(q_host, non_blocking=True)
+            my_len.copy_(len_host, non_blocking=True)
+            new_page_dev.copy_(new_page_host, non_blocking=True)
+            my_tab[rows, used] = new_page_dev
+            step()
+            if rank == 0:
+                out_host.copy_(out, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
         for _ in range(3):
-            _lib.check(L.pkv_decode_splits_only(shard._h, C.byref(a), st))
-        for e0, e1 in evs:
-            e0.record()
-            _lib.check(L.pkv_decode_splits_only(shard._h, C.byref(a), st))
-            e1.record()
-        torch.cuda.synchronize()
-        kern_ms = sum(e0.elapsed_time(e1) for e0, e1 in evs) / len(evs)
-    barrier()
+            e2e_step()
+        e2e_n = 3 if args.lean else max(5, min(steps, 100))
+        e2e_ms = timed(e2e_step, e2e_n) / e2e_n
+        h2d = q_host.numel() * 2 + N * (len_host.numel() * 4 + new_page_host.numel() * 4)
+        e2e = {"value": algo_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": out_host.numel() * 2,
+               "note": "per step, from pinned host memory: q to GPU 0, and to every GPU its shard lengths "
+                       "and one page id per sequence (what a decode step can change; the block tables stay "
+                       "resident); the result is copied back to the host and GPU 0's stream synchronised"}
 
+    # ---- the shard kernel alone on every rank, CUDA events around each launch -------- #
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+           for _ in range(2 if args.lean else 20)]
+    for _ in range(3):
+        _lib.check(L.pkv_decode_splits_only(shard._h, C.byref(a), st))
+    for e0, e1 in evs:
+        e0.record()
+        _lib.check(L.pkv_decode_splits_only(shard._h, C.byref(a), st))
+        e1.record()
+    torch.cuda.synchronize()
+    kern_ms = sum(e0.elapsed_time(e1) for e0, e1 in evs) / len(evs)
+    kern_all = [kern_ms]
+    if N > 1:
+        t = torch.tensor([kern_ms], device=dev)
+        allt = [torch.zeros_like(t) for _ in range(N)]
+        dist.all_gather(allt, t)
+        kern_all = [float(x) for x in allt]
+    barrier()
+    if grp:
+        grp.close()
+    shard.close() if N == 1 else None
+    del pool, view, a
+    wl["pool"] = wl["scales"] = None
+    torch.cuda.empty_cache()
+
+    if rank != 0:
+        return None
+    peak, peak_kind = measured_peak()
+    kern_bytes = local_tokens * bpt
+    achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
+    slowest = max(range(N), key=lambda r: kern_all[r])
+    res = {
+        "value": value, "unit": "GB/s", "steps": steps, "warmup": warm, "ms_per_step": ms_per_step,
+        "us_per_layer": ms_per_step * 1e3, "dtype": wl["dtype"],
+        "config": dict(wl["config"], max_rank_kv_bytes=max(wl["rank_tokens"]) * bpt),
+        "frac_of_aggregate_hbm": value / (peak * N), "frac_of_8tbs_nominal": value / (8000.0 * N),
+        "roofline": {"kernel": "decode_partial_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                     "bytes_per_launch": kern_bytes, "us_per_launch": kern_ms * 1e3,
+                     "traffic": NCU_TRAFFIC_PER_ALGO_BYTE[wl["fmt"]] * kern_bytes},
+        "exchange": {"slowest_shard_kernel_us": kern_all[slowest] * 1e3, "slowest_rank": slowest,
+                     "step_minus_kernel_us": (ms_per_step - kern_all[slowest]) * 1e3,
+                     "frac_of_step": (ms_per_step - kern_all[slowest]) / ms_per_step,
+                     "what": "step time minus the slowest rank's shard kernel timed alone: split-K combine, "
+                             "q publish, partial return, final merge and the launch gap"},
+        "parity": parity,
+        "gpu_launches": launches_per_step * steps,
+        "device_status": status,
+        "rank_ms_per_step": step_rank_ms, "rank_kv_bytes": [t * bpt for t in wl["rank_tokens"]],
+    }
+    if e2e:
+        res["e2e"] = e2e
+    if timeline:
+        res["timeline"] = timeline
+    if clocks is not None:
+        res["clocks"] = dict(clocks, note=f"sampled over the timed steps plus {soak_steps} more identical steps")
+    return res
+
+
+def step_timeline(L, shard, step, barrier, dev, N, rank, reps=5):
+    """%globaltimer stamps of one step in steady state (three untraced steps are queued in
+    front of the traced one, no host synchronisation in between), per rank, in microseconds
+    after that rank's first CTA started.  Median over `reps` traced steps."""
+    import torch
+    import torch.distributed as dist
+    from peerkv_b200 import _lib
+    tr = torch.zeros(1024 * 8, dtype=torch.int64, device=dev)
+    names = ["cta_start_spread", "q_published_or_first_q_seen", "last_tile_consumed", "last_local_combine",
+             "last_peer_tag_seen", "last_row_written"]
+    rows = []
+    for _ in range(reps):
+        barrier()
+        for _ in range(3):
+            step()
+        _lib.check(L.pkv_shard_trace(shard._h, tr.data_ptr()))
+        tr.zero_()
+        step()
+        torch.cuda.synchronize()
+        _lib.check(L.pkv_shard_trace(shard._h, None))
+        t = tr.view(-1, 8).cpu()
+        t = t[t[:, 0] > 0]
+        t0 = int(t[:, 0].min())
+        row = [float(int(t[:, 0].max()) - t0) / 1e3]
+        for w in range(1, 6):
+            col = t[:, w][t[:, w] > 0]
+            row.append(float(int(col.max()) - t0) / 1e3 if col.numel() else None)
+        rows.append(row + [t0])
+    med = []
+    for w in range(6):
+        vals = sorted(r[w] for r in rows if r[w] is not None)
+        med.append(vals[len(vals) // 2] if vals else None)
+    mine = dict(zip(names, med), rank=rank, first_cta_start_ns=rows[-1][6])
+    if N > 1:
+        allr = [None] * N
+        dist.all_gather_object(allr, mine)
+    else:
+        allr = [mine]
+    if rank != 0:
+        return None
+    base = allr[0]["first_cta_start_ns"]
+    for r in allr:      # the GPUs' timers are separate clocks: only a rough cross-rank offset
+        r["first_cta_start_vs_rank0_us"] = (r.pop("first_cta_start_ns") - base) / 1e3
+    return {"unit": "us after the rank's first CTA start; rank 0 is the home GPU", "ranks": allr}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--workload", default="paged-bf16",
+                    choices=list(WORKLOADS) + ["llama-step", "single-fp16"],
+                    help="paged-bf16 is the headline configuration; the others are the remaining "
+                         "benchmark configurations' attention shapes")
+    ap.add_argument("--context", type=int, default=0, help="tokens per sequence, 0 = the workload's own")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the `workloads` block (the other shapes)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="add per-rank device time stamps of one steady-state step to the line")
+    ap.add_argument("--lean", action="store_true", help="timed steps only (for runs under a profiler)")
+    ap.add_argument("--layers", type=int, default=32, help="llama-step only")
+    ap.add_argument("--no-graphs", action="store_true", help="llama-step only: eager launches instead of one graph")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.workload == "llama-step":
+        return run_llama_step(args)
+    if args.workload == "single-fp16":
+        return run_single_layer(args)
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    N = args.gpus
+    if world != N:
+        raise SystemExit(f"--gpus {N} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {N}")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if N > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=dev)
+
+    head = measure_workload(args.workload, args, N, rank, local_rank, dev, args.steps, headline=True)
+    extras = {}
+    if args.workload == "paged-bf16" and not args.no_extra and not args.lean and not args.context:
+        for name in EXTRA_WORKLOADS:
+            r = measure_workload(name, args, N, rank, local_rank, dev, min(args.steps, 20), headline=False)
+            if r is not None:
+                extras[name] = {k: r[k] for k in ("us_per_layer", "value", "unit", "steps", "dtype",
+                                                  "frac_of_aggregate_hbm", "frac_of_8tbs_nominal", "exchange",
+                                                  "parity", "device_status")}
+                extras[name]["kernel_frac_of_peak"] = r["roofline"]["frac"]
+                extras[name]["kv_bytes_per_layer"] = r["config"]["kv_bytes_per_layer"]
+                extras[name]["max_rank_kv_bytes"] = r["config"]["max_rank_kv_bytes"]
+
+    ok = True
     if rank == 0:
-        peak, peak_kind = measured_peak()
-        kern_bytes = local_tokens * bytes_per_token
-        achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
-        line = {
-            "metric": "decode_attn_effective_kv_bandwidth", "value": value, "unit": "GB/s",
-            "n_gpus": N, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-            "us_per_layer": ms_per_step * 1e3, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
-            "config": dict(wl["config"], kv_bytes_per_layer=algo_bytes,
-                           max_rank_kv_bytes=wl["max_rank_tokens"] * bytes_per_token),
-            "frac_of_aggregate_hbm": value / (peak * N), "frac_of_8tbs_nominal": value / (8000.0 * N),
-            "roofline": {"kernel": "decode_partial_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
-                         "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                         "bytes_per_launch": kern_bytes, "us_per_launch": kern_ms * 1e3,
-                         "traffic": (NCU_TRAFFIC_PER_ALGO_BYTE * kern_bytes
-                                     if NCU_TRAFFIC_PER_ALGO_BYTE else None)},
-            "e2e": {"value": algo_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "note": "q, block table and shard lengths copied from pinned host memory, result "
-                            "copied back and the stream synchronised, every step"},
-            "gpu_launches": launches_per_step * args.steps,
-            "clocks": dict(clocks or {}, note=f"sampled over the timed steps plus {soak_steps} more identical steps"),
-            "device_status": status,
-            "rank_ms_per_step": step_rank_ms, "rank_kv_bytes": [t * bytes_per_token for t in wl["rank_tokens"]],
-        }
+        line = {"metric": METRIC, "value": head["value"], "unit": "GB/s", "n_gpus": N, "steps": args.steps,
+                "warmup": head["warmup"], "ms_per_step": head["ms_per_step"], "us_per_layer": head["us_per_layer"],
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": head["dtype"],
+                "data": "synthetic", "config": workload_config(args.workload, N, args.context)}
+        for k in ("frac_of_aggregate_hbm", "frac_of_8tbs_nominal", "roofline", "e2e", "exchange", "parity", "timeline",
+                  "gpu_launches", "clocks", "device_status", "rank_ms_per_step", "rank_kv_bytes"):
+            if k in head:
+                line[k] = head[k]
+        line["max_rank_kv_bytes"] = head["config"]["max_rank_kv_bytes"]
+        if extras:
+            line["workloads"] = extras
+        checks = [head["parity"]] + [e["parity"] for e in extras.values()]
+        ok = all(c is None or c["ok"] for c in checks) and not head["device_status"] and \
+            not any(e["device_status"] for e in extras.values())
         if N == 1 and not args.no_cpu_baseline and not args.lean and args.workload == "paged-bf16":
             cores = os.cpu_count() or 1
             torch.set_num_threads(cores)
+            fns = load_reference()
             tokens = 131072
-            inputs = cpu_sample_inputs(tokens)
-            cpu_reference_step(inputs, 1)
+            inputs = cpu_sample_inputs("paged-bf16", tokens, 1)
+            cpu_reference_step(fns, inputs)
             ts = []
             for _ in range(5):
                 t0 = time.perf_counter()
-                cpu_reference_step(inputs, 1)
+                cpu_reference_step(fns, inputs)
                 ts.append(time.perf_counter() - t0)
             med = sorted(ts)[len(ts) // 2]
+            w = WORKLOADS["paged-bf16"]
             line["cpu_baseline"] = {
-                "value": tokens * BYTES_PER_TOKEN / med / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-                "sample": f"1 of the 16 sequences ({tokens} tokens, 512 MiB of KV): paged gather + GQA "
-                          f"expansion + fp32 attention, median of 5 after 1 warm-up"}
+                "value": tokens * bytes_per_token(w) / med / 1e9, "unit": "GB/s", "cores": cores, "kind": fns[2],
+                "sample": f"1 of the 16 sequences ({tokens} tokens, 512 MiB of KV): the reference's paged gather + "
+                          f"GQA expansion + fp32 attention, median of 5 after 1 warm-up; a rate, extrapolated "
+                          f"to the workload linearly in tokens",
+                "sample_tokens": tokens, "extrapolated": True}
         print(json.dumps(line), flush=True)
-    if grp:
-        grp.close()
+    if N > 1:
+        flag = torch.tensor([1 if ok else 0], device=dev)
+        dist.broadcast(flag, 0)
+        ok = bool(flag.item())
         dist.destroy_process_group()
+    if not ok:
+        raise SystemExit("parity or device status failed: see the JSON line")
 
 
 if __name__ == "__main__":

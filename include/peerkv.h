@@ -152,11 +152,22 @@ int pkv_decode(pkv_shard* s, const pkv_decode_args* a, void* out, int32_t out_dt
  * it -- order them, or use pkv_decode with separate shards. */
 int pkv_decode_static(int device, const pkv_decode_args* a, void* out, int32_t out_dtype,
                       float* lse_out, void* stream);
+/* Reads (and clears) the status word of pkv_decode_static's scratch on `device`;
+ * synchronises `stream` first.  The bits of all static calls since the last read
+ * accumulate.  Allocates nothing.  No counterpart in the reference. */
+int pkv_static_status(int device, void* stream, uint32_t* status_out);
 
 /* Measurement aid: launches ONLY the split-K kernel of pkv_decode (per-CTA partials
  * stay in the shard's scratch, no combine), so its duration can be timed alone with
  * events on `stream`.  No counterpart in the reference. */
 int pkv_decode_splits_only(pkv_shard* s, const pkv_decode_args* a, void* stream);
+/* Measurement aid: every later launch on the shard records %globaltimer stamps per CTA
+ * into buf (device memory of the shard's GPU, 8 x 64-bit words per CTA, room for 1024
+ * CTAs, zeroed by the caller before each launch); NULL switches it off.  Words: 0 CTA
+ * start, 1 query published (home) / first query tag seen (peer), 2 last tile consumed,
+ * 3 last local combine done, 4 last peer tag seen (home), 5 last output row written.
+ * No counterpart in the reference. */
+int pkv_shard_trace(pkv_shard* s, uint64_t* buf);
 
 /* Single-pass N-way LSE merge (replaces merge2_h, csrc/peer_attn_kernels.cuh:64-73,
  * and the fold of umallm/peer_parallel_attn.py:169-172).  Part i is at
@@ -192,11 +203,25 @@ int pkv_split_block_table(int device, const int32_t* block_table, int64_t block_
 
 /* ---- several GPUs ------------------------------------------------------- */
 
-/* Mailboxes of one GPU, allocated once: a q inbox, `world` partial slots
- * ([max_batch, n_q_heads, 128] fp32 O + [max_batch, n_q_heads] lse each) and
- * epoch flags.  rank 0..world-1; the home rank is the one that owns q and runs
- * the merge.  Replaces the per-call stream/event/scratch set-up of
- * csrc/peer_fused_attn_ext.cu:81-97 and its cudaMemcpyAsync hops (:100-101,120-123). */
+/* Mailboxes of one GPU, allocated once: a q inbox with one epoch tag per sequence, and
+ * `world` partial slots ([max_batch, n_q_heads, 128] fp32 O + [max_batch, n_q_heads]
+ * lse each) with one epoch tag per (sequence, q head).  rank 0..world-1; the home rank
+ * is the one that owns q and runs the merge.  Replaces the per-call stream/event/scratch
+ * set-up of csrc/peer_fused_attn_ext.cu:81-97 and its cudaMemcpyAsync hops
+ * (:100-101,120-123).
+ *
+ * Protocol.  Epochs count steps and only grow.  The home GPU stores the query rows of a
+ * sequence into each peer's inbox and then that sequence's tag = epoch; a peer reads the
+ * rows, and writes anything into the home GPU's slot, only after it has seen the tag.
+ * A peer stores the (O, lse) rows of a (sequence, kv-head) into its slot on the home GPU
+ * and then the tags of that group's q heads; the home GPU merges a pair as soon as every
+ * awaited rank's tag for it has arrived.  The home GPU publishes epoch e+1 only after its
+ * merge of epoch e has ended, so neither the inbox nor a slot is rewritten while it can
+ * still be read, also when steps are enqueued back to back without a host
+ * synchronisation.  Every step entry point validates, launches, and only then advances
+ * the epoch: a call that returns an error leaves the epoch unchanged.  All ranks must
+ * issue the same number of steps; after an error, or a step that one rank did not
+ * issue, bring the ranks back together with pkv_exchange_resync. */
 int pkv_exchange_create(pkv_exchange** out, int device, int rank, int world,
                         int max_batch, int n_q_heads);
 int pkv_exchange_destroy(pkv_exchange* x);
@@ -209,28 +234,51 @@ int pkv_exchange_attach(pkv_exchange* x, int peer_rank, pkv_exchange* peer);
 int pkv_exchange_status(pkv_exchange* x, void* stream, uint32_t* status_out);
 /* Current epoch (number of steps begun). */
 int pkv_exchange_epoch(pkv_exchange* x, uint64_t* epoch_out);
+/* Sets the epoch (>= the current one): every rank passes the same value, e.g. the
+ * largest epoch any rank has reached, after a failed or skipped step. */
+int pkv_exchange_resync(pkv_exchange* x, uint64_t epoch);
 
-/* Home rank, start of a step: bumps the epoch, stores q ([batch, n_q_heads, 128],
- * 16-bit) into every attached peer's q inbox with P2P stores and releases their
- * q flag.  Replaces the q broadcast + event fork of peer_fused_attn_ext.cu:100-102,114. */
+/* CUDA-graph capture of a sequence of steps (a whole decode step of L layers as one
+ * graph per GPU, csrc/peer_rt_bench.cu:134-154 and csrc/peer_fused_decoder.cu:433-455 in
+ * the reference).  The kernels take their epoch as `*base + relative`, base being a
+ * device word of the exchange, so a captured launch stays valid on replay:
+ *   pkv_exchange_capture_begin(x);  cudaStreamBeginCapture(stream, ...);
+ *   ... pkv_home_step / pkv_peer_step calls on `stream` ...
+ *   pkv_exchange_capture_end(x, stream, &steps);   -- adds the node that advances base
+ *   cudaStreamEndCapture(stream, &graph);
+ * and after every cudaGraphLaunch of it call pkv_exchange_replayed(x) so that the host's
+ * epoch follows.  Every rank captures the same steps and replays the same number of
+ * times.  No allocation happens in any of these calls. */
+int pkv_exchange_capture_begin(pkv_exchange* x);
+int pkv_exchange_capture_end(pkv_exchange* x, void* stream, uint64_t* steps_out);
+int pkv_exchange_replayed(pkv_exchange* x);
+
+/* Home rank, start of a step in the three-call form (publish, partial, merge): advances
+ * the epoch, stores q ([batch, n_q_heads, 128], 16-bit) into every attached peer's q
+ * inbox with P2P stores and releases the per-sequence tags.  Replaces the q broadcast +
+ * event fork of peer_fused_attn_ext.cu:100-102,114.  pkv_home_step does all three in
+ * one launch and is the form to use. */
 int pkv_home_publish_q(pkv_exchange* x, const void* q, int32_t batch, void* stream);
-/* Peer rank, one step: bumps the epoch, waits (bounded, device side) for the q of
- * this epoch unless q_override is given, computes the shard partial and stores it
- * into the home rank's slot for this rank, then releases the slot's flag.
- * a->q is ignored unless q_override != 0. */
+/* Peer rank, one step: advances the epoch, waits (bounded, device side, per sequence)
+ * for the q of this epoch, computes the shard partial and stores it into the home
+ * rank's slot for this rank, releasing the tags of each (sequence, kv-head) as its rows
+ * are out.  a->q is ignored unless q_override != 0; with q_override the kernel reads
+ * a->q at once and waits for nothing, so the caller must order the step after the home
+ * GPU's previous merge itself. */
 int pkv_peer_step(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, int32_t home_rank,
                   int32_t q_override, void* stream);
-/* Home rank, one whole step in two launches: pkv_home_publish_q, then ONE kernel that
- * streams the home shard, combines its splits and, in its tail, waits (bounded,
- * device side) for the flags of the ranks in wait_mask and folds their partials in.
- * out [batch, n_q_heads, 128] in out_dtype; lse_out may be NULL.  Same result as
- * pkv_home_publish_q + pkv_home_partial + pkv_home_merge with one launch fewer;
- * replaces the host orchestration of csrc/peer_fused_attn_ext.cu:94-135. */
+/* Home rank, one whole step in ONE launch: the kernel's service warps store q into the
+ * peers' inboxes while its other warps already stream the home shard; it combines its
+ * splits and, pair by pair, waits (bounded, device side) for the tags of the ranks in
+ * wait_mask and folds their partials in.  out [batch, n_q_heads, 128] in out_dtype;
+ * lse_out may be NULL.  An empty home pool (n_pages 0) is fine.  Same result as
+ * pkv_home_publish_q + pkv_home_partial + pkv_home_merge; replaces the host
+ * orchestration of csrc/peer_fused_attn_ext.cu:94-135. */
 int pkv_home_step(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, uint32_t wait_mask,
                   void* out, int32_t out_dtype, float* lse_out, void* stream);
 /* Home rank: its own shard's partial into its own slot (after pkv_home_publish_q). */
 int pkv_home_partial(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, void* stream);
-/* Home rank: waits (bounded, device side) for the flags of the ranks in
+/* Home rank: waits (bounded, device side, per row) for the tags of the ranks in
  * `wait_mask` (bit r = wait for rank r; ranks whose work is ordered before this
  * call by stream order or events need no bit), then merges all `world` slots into
  * out [batch, n_q_heads, 128] of out_dtype.  Replaces the event join + merge2_h of

@@ -20,6 +20,8 @@ EXPORTS = [
     "pkv_quantize_kv", "pkv_split_block_table", "pkv_exchange_create", "pkv_exchange_destroy", "pkv_exchange_export",
     "pkv_exchange_import", "pkv_exchange_attach", "pkv_exchange_status", "pkv_exchange_epoch",
     "pkv_home_publish_q", "pkv_home_step", "pkv_peer_step", "pkv_home_partial", "pkv_home_merge",
+    "pkv_static_status", "pkv_shard_trace", "pkv_exchange_resync", "pkv_exchange_capture_begin",
+    "pkv_exchange_capture_end", "pkv_exchange_replayed",
 ]
 
 
@@ -85,6 +87,12 @@ def lib():
         "pkv_peer_step": [vp, vp, P(DecodeArgs), i32, i32, vp],
         "pkv_home_partial": [vp, vp, P(DecodeArgs), vp],
         "pkv_home_merge": [vp, i32, u32, vp, i32, vp, vp],
+        "pkv_static_status": [C.c_int, vp, P(u32)],
+        "pkv_shard_trace": [vp, vp],
+        "pkv_exchange_resync": [vp, u64],
+        "pkv_exchange_capture_begin": [vp],
+        "pkv_exchange_capture_end": [vp, vp, P(u64)],
+        "pkv_exchange_replayed": [vp],
     }
     for name, args in sig.items():
         fn = getattr(L, name)

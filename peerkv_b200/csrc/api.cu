@@ -92,8 +92,8 @@ struct pkv_shard {
   float* part_o = nullptr;
   float* part_ml = nullptr;
   uint32_t* status = nullptr;       // device word
-  unsigned int* done_counter = nullptr;
-  unsigned int* counters = nullptr;  // [n_counter_words]: 64 global words, then per (sequence, kv-head)
+  unsigned int* counters = nullptr;  // [n_counter_words]: 64 spare words, then per (sequence, kv-head)
+  unsigned long long* trace = nullptr;   // caller's time-stamp buffer (pkv_shard_trace), or null
   size_t n_counter_words = 0;
   uint32_t* obs[2] = {nullptr, nullptr};   // per-CTA timings of the last launch / for the next one
   int obs_parity = 0;
@@ -108,9 +108,12 @@ struct pkv_exchange {
   uint8_t* slab = nullptr;                  // this GPU's mailboxes (cudaMalloc)
   uint8_t* peer_slab[pkv::kMaxWorld] = {};  // mapped slabs by rank (own slab at [rank])
   bool imported[pkv::kMaxWorld] = {};       // opened with cudaIpcOpenMemHandle
-  uint32_t* status = nullptr;               // local: status word + counters
-  uint64_t epoch = 0;
-  size_t off_q = 0, off_o = 0, off_lse = 0, off_flags = 0, slab_bytes = 0;
+  uint32_t* status = nullptr;               // local: status word; epoch base at byte 128
+  uint64_t epoch = 0;                       // steps begun (absolute)
+  uint64_t base_host = 0;                   // host mirror of the device-resident epoch base
+  uint64_t cap_epoch0 = 0, cap_steps = 0;   // graph capture: epoch at its start, steps it holds
+  bool capturing = false;
+  size_t off_q = 0, off_qtags = 0, off_o = 0, off_lse = 0, off_tags = 0, slab_bytes = 0;
   size_t o_part_elems = 0, lse_part_elems = 0;
 };
 
@@ -124,8 +127,15 @@ float* slot_o(pkv_exchange* x, int owner_rank, int slot) {
 float* slot_lse(pkv_exchange* x, int owner_rank, int slot) {
   return reinterpret_cast<float*>(x->peer_slab[owner_rank] + x->off_lse) + (size_t)slot * x->lse_part_elems;
 }
-uint64_t* flag_ptr(pkv_exchange* x, int owner_rank, int idx) {   // idx world = q flag
-  return reinterpret_cast<uint64_t*>(x->peer_slab[owner_rank] + x->off_flags) + idx;
+// tags of slot `slot` in rank `owner_rank`'s slab: [max_batch][n_q_heads], same stride as lse
+uint64_t* slot_tags(pkv_exchange* x, int owner_rank, int slot) {
+  return reinterpret_cast<uint64_t*>(x->peer_slab[owner_rank] + x->off_tags) + (size_t)slot * x->lse_part_elems;
+}
+uint64_t* q_tags(pkv_exchange* x, int owner_rank) {               // [max_batch]
+  return reinterpret_cast<uint64_t*>(x->peer_slab[owner_rank] + x->off_qtags);
+}
+uint64_t* epoch_base_dev(pkv_exchange* x) {
+  return reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(x->status) + 128);
 }
 
 }  // namespace
@@ -246,10 +256,10 @@ struct LaunchOut {
   int out_dtype = PKV_F32;
   float* o_part = nullptr;
   float* lse_part = nullptr;
-  uint64_t* done_flag = nullptr;
-  uint64_t done_epoch = 0;
-  const uint64_t* q_flag = nullptr;
-  uint64_t q_epoch = 0;
+  uint64_t* part_tags = nullptr;      // released per (sequence, kv-head) after its rows
+  const uint64_t* q_tags = nullptr;   // peer: wait for the query rows of this epoch
+  const uint64_t* epoch_base = nullptr;
+  uint64_t epoch_rel = 0;
   bool skip_combine = false;
   pkv_exchange* home = nullptr;   // set: publish q, wait for the peers and merge in the same kernel
   uint32_t wait_mask = 0;
@@ -314,9 +324,13 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   p.part_o = s->part_o;
   p.part_ml = s->part_ml;
   p.status = s->status;
-  p.q_flag = lo.q_flag;
-  p.q_epoch = lo.q_epoch;
+  p.q_tags = lo.q_tags;
+  p.epoch_base = lo.epoch_base;
+  p.epoch_rel = lo.epoch_rel;
   p.q_timeout_ns = kWaitNs;
+  p.part_tags = lo.part_tags;
+  p.force_empty = kv.n_pages > 0 ? 0 : 1;
+  p.trace = s->trace;
   p.k_scale = kv.k_scale;
   p.v_scale = kv.v_scale;
   p.fuse = lo.skip_combine ? 0 : 1;
@@ -327,9 +341,6 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   p.seq_counter = s->counters + 64;
   p.grp_counter = s->counters + s->grp_counter_off;
   p.grp_slot0 = s->grp_slot0;
-  p.all_counter = s->counters;
-  p.done_flag = lo.done_flag;
-  p.done_epoch = lo.done_epoch;
   if (s->obs[0] && n_cta_x <= pkv::kMaxCtas) {
     p.obs_read = s->obs[s->obs_parity];
     p.obs_write = s->obs[s->obs_parity ^ 1];
@@ -344,61 +355,47 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
     p.mg_lse = slot_lse(x, x->rank, 0);
     p.mg_o_stride = (int64_t)x->o_part_elems;
     p.mg_lse_stride = (int64_t)x->lse_part_elems;
-    p.mg_flags = flag_ptr(x, x->rank, 0);
-    p.mg_epoch = x->epoch;
+    p.mg_tags = slot_tags(x, x->rank, 0);
+    p.mg_tag_stride = (int64_t)x->lse_part_elems;
     p.mg_timeout_ns = kWaitNs;
     p.mg_status = x->status;
+    for (int r = 0; r < x->world; ++r) {
+      if (r == x->rank) continue;
+      p.pub_q[p.pub_n] = reinterpret_cast<uint4*>(x->peer_slab[r] + x->off_q);
+      p.pub_tags[p.pub_n] = q_tags(x, r);
+      ++p.pub_n;
+    }
   }
 
+  // An empty pool goes through the same kernel: every sequence counts as empty, no tile is
+  // ever loaded (the zeroed tensor maps are not touched), and the service warps write the
+  // neutral rows (O = 0, lse = -inf) or, on the home GPU, the merge of the peers' rows.
+  CUtensorMap tk, tv;
+  memset(&tk, 0, sizeof tk);
+  memset(&tv, 0, sizeof tv);
   if (kv.n_pages > 0) {
-    CUtensorMap tk, tv;
     rc = build_map(s, kv.k, kv, &tk);
     if (rc) return rc;
     rc = build_map(s, kv.v, kv, &tv);
     if (rc) return rc;
-    dim3 grid(n_cta_x, n_hb);
-    const dim3 block(pkv::cta_threads(is_quant(kv.dtype) ? kWphQ : 1));
-    const bool qbf = a->q_dtype == PKV_BF16;
-    switch (kv.dtype) {
-      case PKV_BF16: pkv::decode_partial_kernel<pkv::kKvBF16, true, kStages, 1><<<grid, block, L16::kTotal, st>>>(tk, tv, p); break;
-      case PKV_F16: pkv::decode_partial_kernel<pkv::kKvF16, false, kStages, 1><<<grid, block, L16::kTotal, st>>>(tk, tv, p); break;
-      case PKV_INT8:
-        if (qbf) pkv::decode_partial_kernel<pkv::kKvInt8, true, kStagesQ, kWphQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
-        else     pkv::decode_partial_kernel<pkv::kKvInt8, false, kStagesQ, kWphQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
-        break;
-      default:
-        if (qbf) pkv::decode_partial_kernel<pkv::kKvFp8, true, kStagesQ, kWphQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
-        else     pkv::decode_partial_kernel<pkv::kKvFp8, false, kStagesQ, kWphQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
-        break;
-    }
-    PKV_CUDA(cudaGetLastError());
-    return PKV_OK;   // the combine is fused into the kernel's tail
   }
-
-  // An empty pool: only the neutral rows (O = 0, lse = -inf) and the completion flag.
-  if (lo.skip_combine) return PKV_OK;
-  pkv::CombineParams c;
-  memset(&c, 0, sizeof c);
-  c.seq_lens = a->seq_lens;
-  c.part_o = s->part_o;
-  c.part_ml = s->part_ml;
-  c.batch = a->batch;
-  c.n_q_heads = a->n_q_heads;
-  c.page_size = kv.page_size;
-  c.tiles_per_page = p.tiles_per_page;
-  c.n_cta_x = n_cta_x;
-  c.out = lo.out;
-  c.out_dtype = lo.out_dtype;
-  c.o_part = lo.o_part;
-  c.lse_part = lo.lse_part;
-  c.done_counter = s->done_counter;
-  c.done_flag = lo.done_flag;
-  c.done_epoch = lo.done_epoch;
-  c.status = s->status;
-  dim3 cgrid(a->batch, (a->n_q_heads + pkv::kCombineHeads - 1) / pkv::kCombineHeads);
-  pkv::decode_combine_kernel<<<cgrid, 128 * pkv::kCombineHeads, (a->batch + 1) * sizeof(int), st>>>(c);
+  dim3 grid(n_cta_x, n_hb);
+  const dim3 block(pkv::cta_threads(is_quant(kv.dtype) ? kWphQ : 1));
+  const bool qbf = a->q_dtype == PKV_BF16;
+  switch (kv.dtype) {
+    case PKV_BF16: pkv::decode_partial_kernel<pkv::kKvBF16, true, kStages, 1><<<grid, block, L16::kTotal, st>>>(tk, tv, p); break;
+    case PKV_F16: pkv::decode_partial_kernel<pkv::kKvF16, false, kStages, 1><<<grid, block, L16::kTotal, st>>>(tk, tv, p); break;
+    case PKV_INT8:
+      if (qbf) pkv::decode_partial_kernel<pkv::kKvInt8, true, kStagesQ, kWphQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
+      else     pkv::decode_partial_kernel<pkv::kKvInt8, false, kStagesQ, kWphQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
+      break;
+    default:
+      if (qbf) pkv::decode_partial_kernel<pkv::kKvFp8, true, kStagesQ, kWphQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
+      else     pkv::decode_partial_kernel<pkv::kKvFp8, false, kStagesQ, kWphQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
+      break;
+  }
   PKV_CUDA(cudaGetLastError());
-  return PKV_OK;
+  return PKV_OK;   // the combine is fused into the kernel's tail
 }
 
 int read_status(int device, uint32_t* dev_word, cudaStream_t st, uint32_t* out) {
@@ -462,7 +459,6 @@ int pkv_shard_create(pkv_shard** out, int device, int max_batch, int n_q_heads) 
     pkv_shard_destroy(s);
     return fail(PKV_E_CUDA, "scratch allocation failed: %s", cudaGetErrorString(e));
   }
-  s->done_counter = reinterpret_cast<unsigned int*>(s->status) + 16;
   *out = s;
   return PKV_OK;
 }
@@ -488,7 +484,6 @@ int pkv_shard_status(pkv_shard* s, void* stream, uint32_t* status_out) {
     DeviceGuard guard(s->device);
     PKV_CUDA(cudaMemsetAsync(s->counters, 0, s->n_counter_words * sizeof(unsigned int),
                              static_cast<cudaStream_t>(stream)));
-    PKV_CUDA(cudaMemsetAsync(s->done_counter, 0, sizeof(unsigned int), static_cast<cudaStream_t>(stream)));
     PKV_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   }
   if (status_out) *status_out = v;
@@ -620,8 +615,9 @@ int pkv_exchange_create(pkv_exchange** out, int device, int rank, int world, int
   x->off_q = 0;
   x->off_o = align_up((size_t)max_batch * n_q_heads * pkv::kHeadDim * 2, 256);
   x->off_lse = x->off_o + align_up(world * x->o_part_elems * sizeof(float), 256);
-  x->off_flags = x->off_lse + align_up(world * x->lse_part_elems * sizeof(float), 256);
-  x->slab_bytes = x->off_flags + align_up((world + 1) * sizeof(uint64_t), 256);
+  x->off_tags = x->off_lse + align_up(world * x->lse_part_elems * sizeof(float), 256);
+  x->off_qtags = x->off_tags + align_up(world * x->lse_part_elems * sizeof(uint64_t), 256);
+  x->slab_bytes = x->off_qtags + align_up((size_t)max_batch * sizeof(uint64_t), 256);
   cudaError_t e = cudaMalloc(&x->slab, x->slab_bytes);
   if (e == cudaSuccess) e = cudaMemset(x->slab, 0, x->slab_bytes);
   if (e == cudaSuccess) e = cudaMalloc(&x->status, 512);
@@ -703,29 +699,84 @@ int pkv_exchange_epoch(pkv_exchange* x, uint64_t* epoch_out) {
   return PKV_OK;
 }
 
+int pkv_exchange_resync(pkv_exchange* x, uint64_t epoch) {
+  if (!x) return fail(PKV_E_INVALID, "null exchange");
+  if (x->capturing) return fail(PKV_E_STATE, "resync during a graph capture");
+  if (epoch < x->epoch) return fail(PKV_E_INVALID, "epochs only grow: %llu < %llu",
+                                    (unsigned long long)epoch, (unsigned long long)x->epoch);
+  x->epoch = epoch;
+  return PKV_OK;
+}
+
+int pkv_exchange_capture_begin(pkv_exchange* x) {
+  if (!x) return fail(PKV_E_INVALID, "null exchange");
+  if (x->capturing) return fail(PKV_E_STATE, "capture already begun");
+  x->capturing = true;
+  x->cap_epoch0 = x->epoch;
+  return PKV_OK;
+}
+
+int pkv_exchange_capture_end(pkv_exchange* x, void* stream, uint64_t* steps_out) {
+  if (!x) return fail(PKV_E_INVALID, "null exchange");
+  if (!x->capturing) return fail(PKV_E_STATE, "no capture begun");
+  DeviceGuard guard(x->device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", x->device);
+  const uint64_t steps = x->epoch - x->cap_epoch0;
+  // last node of the captured step: the next replay's epochs start where this one's end
+  pkv::bump_epoch_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(epoch_base_dev(x), steps);
+  PKV_CUDA(cudaGetLastError());
+  x->capturing = false;
+  x->cap_steps = steps;
+  x->epoch = x->cap_epoch0;     // nothing has run yet: a capture only records
+  if (steps_out) *steps_out = steps;
+  return PKV_OK;
+}
+
+int pkv_exchange_replayed(pkv_exchange* x) {
+  if (!x) return fail(PKV_E_INVALID, "null exchange");
+  if (x->capturing || !x->cap_steps) return fail(PKV_E_STATE, "no captured step to account for");
+  x->epoch += x->cap_steps;
+  x->base_host += x->cap_steps;
+  return PKV_OK;
+}
+
+namespace {
+int check_step(pkv_exchange* x, const pkv_decode_args* a) {
+  if (a->batch <= 0 || a->batch > x->max_batch)
+    return fail(PKV_E_INVALID, "batch %d outside [1, %d]", a->batch, x->max_batch);
+  if (a->n_q_heads != x->n_q_heads) return fail(PKV_E_INVALID, "n_q_heads mismatch");
+  return PKV_OK;
+}
+}  // namespace
+
+// Every step entry point validates first, launches, and only then commits the new epoch:
+// a call that fails leaves the exchange where it was.
 int pkv_home_publish_q(pkv_exchange* x, const void* q, int32_t batch, void* stream) {
   if (!x || !q) return fail(PKV_E_INVALID, "null pointer");
   if (batch <= 0 || batch > x->max_batch) return fail(PKV_E_INVALID, "batch %d", batch);
   if (reinterpret_cast<uintptr_t>(q) & 15) return fail(PKV_E_INVALID, "q must be 16-byte aligned");
-  x->epoch += 1;
   pkv::PublishParams p;
   memset(&p, 0, sizeof p);
   p.q = static_cast<const uint4*>(q);
-  p.n16 = (int64_t)batch * x->n_q_heads * pkv::kHeadDim * 2 / 16;
-  p.epoch = x->epoch;
+  p.batch = batch;
+  p.row16 = x->n_q_heads * (pkv::kHeadDim * 2 / 16);
+  p.epoch_base = epoch_base_dev(x);
+  p.epoch_rel = x->epoch + 1 - x->base_host;
   int n = 0;
   for (int r = 0; r < x->world; ++r) {
     if (r == x->rank) continue;
     if (!x->peer_slab[r]) return fail(PKV_E_STATE, "rank %d is not attached", r);
     p.dst[n] = reinterpret_cast<uint4*>(x->peer_slab[r] + x->off_q);
-    p.flag[n] = flag_ptr(x, r, x->world);
+    p.tags[n] = q_tags(x, r);
     ++n;
   }
-  if (n == 0) return PKV_OK;
-  DeviceGuard guard(x->device);
-  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", x->device);
-  pkv::publish_q_kernel<<<n, 1024, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  PKV_CUDA(cudaGetLastError());
+  if (n > 0) {
+    DeviceGuard guard(x->device);
+    if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", x->device);
+    pkv::publish_q_kernel<<<n, 1024, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    PKV_CUDA(cudaGetLastError());
+  }
+  x->epoch += 1;
   return PKV_OK;
 }
 
@@ -735,27 +786,29 @@ int pkv_peer_step(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, int32
   if (home_rank < 0 || home_rank >= x->world || home_rank == x->rank)
     return fail(PKV_E_INVALID, "home_rank %d", home_rank);
   if (!x->peer_slab[home_rank]) return fail(PKV_E_STATE, "home rank %d is not attached", home_rank);
-  if (a->batch <= 0 || a->batch > x->max_batch) return fail(PKV_E_INVALID, "batch %d", a->batch);
-  if (a->n_q_heads != x->n_q_heads) return fail(PKV_E_INVALID, "n_q_heads mismatch");
-  x->epoch += 1;
+  int rc = check_step(x, a);
+  if (rc) return rc;
   pkv_decode_args aa = *a;
   LaunchOut lo;
+  lo.epoch_base = epoch_base_dev(x);
+  lo.epoch_rel = x->epoch + 1 - x->base_host;
   if (!q_override) {
     aa.q = x->slab + x->off_q;
-    lo.q_flag = flag_ptr(x, x->rank, x->world);
-    lo.q_epoch = x->epoch;
+    lo.q_tags = q_tags(x, x->rank);
   }
   lo.o_part = slot_o(x, home_rank, x->rank);
   lo.lse_part = slot_lse(x, home_rank, x->rank);
-  lo.done_flag = flag_ptr(x, home_rank, x->rank);
-  lo.done_epoch = x->epoch;
-  return launch_decode(s, &aa, lo, static_cast<cudaStream_t>(stream));
+  lo.part_tags = slot_tags(x, home_rank, x->rank);
+  rc = launch_decode(s, &aa, lo, static_cast<cudaStream_t>(stream));
+  if (rc) return rc;
+  x->epoch += 1;
+  return PKV_OK;
 }
 
 int pkv_home_partial(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, void* stream) {
   if (!x || !s || !a) return fail(PKV_E_INVALID, "null pointer");
-  if (a->batch <= 0 || a->batch > x->max_batch) return fail(PKV_E_INVALID, "batch %d", a->batch);
-  if (a->n_q_heads != x->n_q_heads) return fail(PKV_E_INVALID, "n_q_heads mismatch");
+  int rc = check_step(x, a);
+  if (rc) return rc;
   LaunchOut lo;
   lo.o_part = slot_o(x, x->rank, x->rank);
   lo.lse_part = slot_lse(x, x->rank, x->rank);
@@ -765,29 +818,25 @@ int pkv_home_partial(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, vo
 int pkv_home_step(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, uint32_t wait_mask,
                   void* out, int32_t out_dtype, float* lse_out, void* stream) {
   if (!x || !s || !a || !out) return fail(PKV_E_INVALID, "null pointer");
-  if (a->batch <= 0 || a->batch > x->max_batch) return fail(PKV_E_INVALID, "batch %d", a->batch);
-  if (a->n_q_heads != x->n_q_heads) return fail(PKV_E_INVALID, "n_q_heads mismatch");
+  int rc = check_step(x, a);
+  if (rc) return rc;
   if (out_dtype != PKV_F16 && out_dtype != PKV_BF16 && out_dtype != PKV_F32)
     return fail(PKV_E_INVALID, "out_dtype %d", out_dtype);
   if (reinterpret_cast<uintptr_t>(a->q) & 15) return fail(PKV_E_INVALID, "q must be 16-byte aligned");
   for (int r = 0; r < x->world; ++r)
     if (!x->peer_slab[r]) return fail(PKV_E_STATE, "rank %d is not attached", r);
-  if (a->kv.n_pages == 0) {
-    // nothing of the KV lives here: the three-kernel form covers it
-    int rc = pkv_home_publish_q(x, a->q, a->batch, stream);
-    if (!rc) rc = pkv_home_partial(x, s, a, stream);
-    if (!rc) rc = pkv_home_merge(x, a->batch, wait_mask, out, out_dtype, lse_out, stream);
-    return rc;
-  }
-  int rc = pkv_home_publish_q(x, a->q, a->batch, stream);   // bumps the epoch
-  if (rc) return rc;
   LaunchOut lo;
   lo.out = out;
   lo.out_dtype = out_dtype;
   lo.lse_part = lse_out;
   lo.home = x;
   lo.wait_mask = wait_mask;
-  return launch_decode(s, a, lo, static_cast<cudaStream_t>(stream));
+  lo.epoch_base = epoch_base_dev(x);
+  lo.epoch_rel = x->epoch + 1 - x->base_host;
+  rc = launch_decode(s, a, lo, static_cast<cudaStream_t>(stream));
+  if (rc) return rc;
+  x->epoch += 1;
+  return PKV_OK;
 }
 
 int pkv_home_merge(pkv_exchange* x, int32_t batch, uint32_t wait_mask, void* out,
@@ -807,13 +856,21 @@ int pkv_home_merge(pkv_exchange* x, int32_t batch, uint32_t wait_mask, void* out
   m.n_parts = x->world;
   m.rows = batch * x->n_q_heads;
   m.out = out; m.out_dtype = out_dtype; m.lse_out = lse_out;
-  m.flags = flag_ptr(x, x->rank, 0);
+  m.tags = slot_tags(x, x->rank, 0);
+  m.tag_stride = (int64_t)x->lse_part_elems;
   m.wait_mask = wait_mask & ~(1u << x->rank);
-  m.epoch = x->epoch;
+  m.epoch_base = epoch_base_dev(x);
+  m.epoch_rel = x->epoch - x->base_host;
   m.timeout_ns = kWaitNs;
   m.status = x->status;
   pkv::merge_partials_kernel<<<(m.rows + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(m);
   PKV_CUDA(cudaGetLastError());
+  return PKV_OK;
+}
+
+int pkv_shard_trace(pkv_shard* s, uint64_t* buf) {
+  if (!s) return fail(PKV_E_INVALID, "null shard");
+  s->trace = reinterpret_cast<unsigned long long*>(buf);
   return PKV_OK;
 }
 
@@ -872,7 +929,6 @@ int static_setup(int device) {
   s.part_o = po;
   s.part_ml = pml;
   s.status = reinterpret_cast<uint32_t*>(pw);          // words [0, 64): status block
-  s.done_counter = pw + 16;
   s.counters = pw + 64;                                // 64 global words, then per (sequence, kv-head)
   s.n_counter_words = kStaticWords - 64;
   s.grp_counter_off = kStaticGrpOff;
@@ -906,9 +962,10 @@ extern "C" int pkv_decode_static(int device, const pkv_decode_args* a, void* out
   if (rc) return rc;
   pkv_shard& s = g_static_shard[device];
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // The arrays keep whatever the previous call left: status and arrival counters must
-  // start at zero (a call that gave up on a wait may have left them half-counted).
-  PKV_CUDA(cudaMemsetAsync(s.status, 0, kStaticWords * sizeof(unsigned int), st));
+  // The arrays keep whatever the previous call left: the arrival counters must start at
+  // zero (a call that gave up on a wait may have left them half-counted).  The status
+  // word is left alone: its bits stay until pkv_static_status reads them.
+  PKV_CUDA(cudaMemsetAsync(s.counters, 0, s.n_counter_words * sizeof(unsigned int), st));
   std::lock_guard<std::mutex> lock(g_static_mutex);
   s.n_q_heads = a->n_q_heads;
   LaunchOut lo;
@@ -916,4 +973,13 @@ extern "C" int pkv_decode_static(int device, const pkv_decode_args* a, void* out
   lo.out_dtype = out_dtype;
   lo.lse_part = lse_out;
   return launch_decode(&s, a, lo, st);
+}
+
+extern "C" int pkv_static_status(int device, void* stream, uint32_t* status_out) {
+  if (device < 0 || device >= kStaticMaxDevices) return fail(PKV_E_INVALID, "device %d", device);
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", device);
+  int rc = static_setup(device);
+  if (rc) return rc;
+  return read_status(device, g_static_shard[device].status, static_cast<cudaStream_t>(stream), status_out);
 }

@@ -10,7 +10,8 @@
 // tokens, not by sequences.  Where a range crosses a sequence boundary the CTA
 // flushes one partial (unnormalised O, running max m, running sum l) to slot
 // c + seq; a sequence is therefore covered by the consecutive slots of the CTAs
-// that touched it and decode_combine_kernel merges them.
+// that touched it, and the warp that finishes a (sequence, kv-head) last merges them in
+// the kernel's tail (replaces attn_combine, csrc/peer_attn_kernels.cuh:50-61).
 //
 // Inside a CTA: warps 8 and 9 are the producers of a K ring and a V ring of 32 KiB
 // slots; 16 lanes each issue one 2 KiB TMA box per tile (8 heads x 2 halves of the
@@ -52,6 +53,9 @@ enum : uint32_t {
   kStPartialTimeout = 0x8u,
 };
 
+constexpr int kMaxWorld = 16;       // ranks of one exchange
+constexpr int kTraceWords = 8;      // 64-bit time stamps per CTA when a trace buffer is given
+
 struct DecodeParams {
   const void* q;               // [B][Hq][128] 16-bit
   const int32_t* block_table;  // may be null (identity)
@@ -68,12 +72,18 @@ struct DecodeParams {
   int tiles_per_page;  // ceil(page_size / 16)
   int head_major;      // 1: pool dims are (d, tok, head, page); 0: (d, head, tok, page)
   int n_cta_x;
+  int force_empty;     // 1: the pool holds no page; every sequence counts as empty here
   float scale_log2;    // softmax scale * log2(e)
   float* part_o;       // [slots][Hq][128]
   float* part_ml;      // [slots][Hq][2]  (m in log2 units, l)
   uint32_t* status;
-  const uint64_t* q_flag;  // null, or: wait until *q_flag >= q_epoch before reading q
-  uint64_t q_epoch;
+  // Epochs are `*epoch_base + <relative value>`: the base is a device word that a captured
+  // graph bumps once per replay, so the same launch parameters stay valid.  Null = 0.
+  const uint64_t* epoch_base;
+  // peer rank: sequence s may be read from q, and its rows written to the home GPU, once
+  // q_tags[s] >= epoch (the home GPU stores the tag after the rows of q).  Null: q is local.
+  const uint64_t* q_tags;
+  uint64_t epoch_rel;
   uint64_t q_timeout_ns;
   // fused combine: the last CTA to finish a sequence merges that sequence's slots
   int fuse;                    // 0: leave the per-CTA partials in part_o / part_ml
@@ -81,29 +91,52 @@ struct DecodeParams {
   void* out;                   // [B][Hq][128] final output, or null
   float* o_part;               // [B][Hq][128] f32 normalised shard partial, or null (may be P2P)
   float* lse_part;             // [B][Hq] natural log, or null (may be P2P)
+  uint64_t* part_tags;         // [B][Hq] or null: after the rows of (sequence, kv-head) are out, the
+                               // tags of that group's q heads are released with the epoch (may be P2P)
   unsigned int* seq_counter;   // [batch][n_kv_heads], zero between launches
   unsigned int* grp_counter;   // [(CTA groups + batch)][n_kv_heads], zero between launches
   int grp_slot0;               // first slot index of the per-group partials
-  unsigned int* all_counter;   // sequences finished, zero between launches
-  uint64_t* done_flag;         // released with done_epoch when every sequence is out (may be P2P)
-  uint64_t done_epoch;
   // adaptive split of the tile list: per-CTA (duration ns, tiles, weight) of the previous
   // launch on this shard; written for the next one.  Word 0 is the CTA count they refer to.
   const uint32_t* obs_read;
   uint32_t* obs_write;
+  // home GPU only -- q publish in the prologue: the service warps store q [B][Hq][128] into
+  // every peer's inbox and release that peer's per-sequence q tags.
+  int pub_n;
+  uint4* pub_q[kMaxWorld];
+  uint64_t* pub_tags[kMaxWorld];
   // home GPU only -- final merge in the tail: after a (sequence, kv-head) is combined locally
-  // the same warp waits (bounded) for the peers' flags and folds their (O, lse) rows in.
+  // the same warp waits (bounded) for the peers' tags of that pair and folds their rows in.
   int mg_n;                    // partial slots (ranks); 0 = no merge
   int mg_self;                 // this rank's slot (its own rows never leave the registers)
-  uint32_t mg_wait_mask;       // bit r: wait for mg_flags[r] >= mg_epoch
+  uint32_t mg_wait_mask;       // bit r: wait for rank r's tags
   const float* mg_o;           // slot r at mg_o + r * mg_o_stride: [B][Hq][128]
   const float* mg_lse;         // slot r at mg_lse + r * mg_lse_stride: [B][Hq]
-  int64_t mg_o_stride, mg_lse_stride;
-  const uint64_t* mg_flags;
-  uint64_t mg_epoch;
+  const uint64_t* mg_tags;     // slot r at mg_tags + r * mg_tag_stride: [B][Hq]
+  int64_t mg_o_stride, mg_lse_stride, mg_tag_stride;
   uint64_t mg_timeout_ns;
   uint32_t* mg_status;         // the exchange's status word
+  // measurement aid: [CTAs][kTraceWords] %globaltimer stamps, or null
+  //   0 CTA start   1 q published (home) / first q tag seen (peer)   2 last tile consumed
+  //   3 last local combine done   4 last peer tag seen (home)   5 last row written
+  unsigned long long* trace;
 };
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void trace_max(const DecodeParams& p, int word) {
+  if (p.trace)
+    atomicMax(p.trace + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * kTraceWords + word, global_ns());
+}
+__device__ __forceinline__ void trace_first(const DecodeParams& p, int word) {
+  if (p.trace) {
+    unsigned long long* w = p.trace + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * kTraceWords + word;
+    atomicCAS(w, 0ull, global_ns());
+  }
+}
 
 // Tiles of a sequence with `len` tokens in this shard.
 __device__ __forceinline__ int seq_tiles(int len, int page_size, int tiles_per_page) {
@@ -115,10 +148,10 @@ __device__ __forceinline__ int seq_tiles(int len, int page_size, int tiles_per_p
 // Exclusive prefix of tiles per sequence into smem `prefix[0..batch]`.
 // Called by all threads of the block; ends with a __syncthreads().
 __device__ __forceinline__ void build_tile_prefix(int* prefix, const int32_t* seq_lens, int batch,
-                                                  int page_size, int tiles_per_page) {
+                                                  int page_size, int tiles_per_page, bool force_empty) {
   const int tid = threadIdx.x, nthr = blockDim.x;
   for (int b = tid; b < batch; b += nthr) {
-    int len = seq_lens[b];
+    int len = force_empty ? 0 : seq_lens[b];
     prefix[b + 1] = len > 0 ? seq_tiles(len, page_size, tiles_per_page) : 0;
   }
   if (tid == 0) prefix[0] = 0;
@@ -149,12 +182,6 @@ __device__ __forceinline__ int find_seq(const int* prefix, int batch, int g) {
     if (prefix[mid] <= g) lo = mid; else hi = mid;
   }
   return lo;
-}
-
-__device__ __forceinline__ void store_out(void* out, int dtype, int64_t idx, float v) {
-  if (dtype == 4) reinterpret_cast<float*>(out)[idx] = v;
-  else if (dtype == 1) reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
-  else reinterpret_cast<__half*>(out)[idx] = __float2half_rn(v);
 }
 
 __device__ __forceinline__ void store_out4(void* out, int dtype, int64_t idx, float4 v) {
@@ -287,39 +314,83 @@ __device__ __forceinline__ void combine_group(const DecodeParams& p, int b, int 
   }
 }
 
-// Bounded wait of one warp for the peers' completion flags (lane r polls rank r).
-// Returns false, with the status bit set, if a flag did not reach the epoch in time.
-__device__ __forceinline__ bool wait_peer_flags(const DecodeParams& p, int lane) {
+// Bounded wait of one warp for the peers' tags of one row (lane r polls rank r).  Returns
+// false, with the status bit set, if a tag did not reach the epoch in time; once one wait
+// has run out, later waits of the same launch give up at once.
+__device__ __forceinline__ bool wait_peer_tags(const DecodeParams& p, uint64_t epoch, int64_t row,
+                                               int lane) {
   bool ok = true;
   if (lane < p.mg_n && ((p.mg_wait_mask >> lane) & 1u)) {
-    uint64_t t0, now;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    const uint64_t* tag = p.mg_tags + lane * p.mg_tag_stride + row;
+    const unsigned long long t0 = global_ns();
     for (;;) {
-      if (ld_acquire_sys_u64(p.mg_flags + lane) >= p.mg_epoch) break;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-      if (now - t0 > p.mg_timeout_ns) { ok = false; break; }
-      __nanosleep(64);
+      if (ld_acquire_sys_u64(tag) >= epoch) break;
+      if ((*reinterpret_cast<const volatile uint32_t*>(p.mg_status) & kStPartialTimeout) ||
+          global_ns() - t0 > p.mg_timeout_ns) { ok = false; break; }
+      __nanosleep(32);
     }
     if (!ok) atomicOr(p.mg_status, kStPartialTimeout);
   }
-  return __all_sync(0xffffffffu, ok);
+  ok = __all_sync(0xffffffffu, ok);
+  if (lane == 0) trace_max(p, 4);
+  return ok;
 }
 
-// Counts `n` finished (sequence, kv-head) units; whoever completes the count
-// re-arms the counter and releases the completion flag (unless a wait timed out).
-__device__ __forceinline__ void count_done(const DecodeParams& p, unsigned int n,
-                                           unsigned int expected) {
-  const unsigned int prev = atomicAdd(p.all_counter, n);
-  if (prev + n == expected) {
-    *p.all_counter = 0;
-    if (p.done_flag) {
-      const uint32_t bad = *reinterpret_cast<const volatile uint32_t*>(p.status) &
-                           (kStPipeTimeout | kStQTimeout);
-      if (!bad) {
-        __threadfence_system();
-        st_release_sys_u64(p.done_flag, p.done_epoch);
+// Bounded wait of one warp for the query rows of sequence s (peer ranks).  The home GPU
+// stores the tag after the rows, so the rows may be read once this returns true -- and,
+// because the home GPU publishes epoch e only after its merge of epoch e-1 has ended,
+// this rank's slot on the home GPU may be overwritten from then on as well.
+__device__ __forceinline__ bool wait_q_tag(const DecodeParams& p, uint64_t epoch, int s, int lane,
+                                           volatile int* abort_flag) {
+  int ok = 1;
+  if (lane == 0) {
+    ok = 0;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+      if (ld_acquire_sys_u64(p.q_tags + s) >= epoch) { ok = 1; break; }
+      if (*abort_flag) break;                       // the CTA gave up elsewhere: just leave
+      if (global_ns() - t0 > p.q_timeout_ns) {
+        atomicOr(p.status, kStQTimeout);
+        *abort_flag = 1;
+        break;
       }
+      __nanosleep(64);
     }
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  __syncwarp();
+  return ok != 0;
+}
+
+// After a warp has written the rows of (sequence b, q heads qh0 .. qh0+nq-1): make them
+// visible system-wide, then release the tags of those heads.  One tag of the group proves
+// all of the group's rows (the fence of every lane and the warp barrier come first).
+__device__ __forceinline__ void release_unit(const DecodeParams& p, uint64_t epoch, int b, int qh0,
+                                             int nq, int lane) {
+  if (lane == 0) trace_max(p, 5);
+  if (!p.part_tags) return;
+  __threadfence_system();
+  __syncwarp();
+  if (lane < nq) st_release_sys_u64(p.part_tags + (int64_t)b * p.n_q_heads + qh0 + lane, epoch);
+}
+
+// An on-chip wait ended without its barrier: unless the CTA had already aborted for
+// another reason (a query that never came), that is a pipeline time-out.
+__device__ __forceinline__ void pipe_failed(const DecodeParams& p, volatile int* abort_flag) {
+  if (!*abort_flag) {
+    atomicOr(p.status, kStPipeTimeout);
+    *abort_flag = 1;
+  }
+}
+
+// Waits for a phase of an on-chip barrier.  Gives up when the CTA has aborted or the
+// deadline (%globaltimer) has passed.
+__device__ __forceinline__ bool pipe_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long deadline) {
+  for (uint32_t w = 0;; ++w) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if ((w & 63u) == 63u && global_ns() > deadline) return false;
   }
 }
 
@@ -518,7 +589,9 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
     *abort_flag = 0;
     fence_barrier_init();
   }
-  build_tile_prefix(prefix, p.seq_lens, p.batch, p.page_size, p.tiles_per_page);
+  build_tile_prefix(prefix, p.seq_lens, p.batch, p.page_size, p.tiles_per_page, p.force_empty != 0);
+  const uint64_t epoch = (p.epoch_base ? *reinterpret_cast<const volatile uint64_t*>(p.epoch_base) : 0ull) +
+                         p.epoch_rel;
 
   const int total = prefix[p.batch];
   int* bound = reinterpret_cast<int*>(sgen + L::kBoundOff);
@@ -526,8 +599,11 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
   build_cta_bounds(bound, cta_weight, total, p.n_cta_x, p.obs_read);
   const int g0 = bound[blockIdx.x];
   const int g1 = bound[blockIdx.x + 1];
-  unsigned long long t_start;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_start));
+  const unsigned long long t_start = global_ns();
+  // every on-chip wait ends by then: the longest legitimate stall (a peer whose query is
+  // late) plus two seconds
+  const unsigned long long pipe_deadline = t_start + p.q_timeout_ns + 2000000000ull;
+  if (threadIdx.x == 0) trace_first(p, 0);
   if (p.obs_write && warp == 0 && lane == 0 && blockIdx.y == 0) {
     if (blockIdx.x == 0) p.obs_write[0] = (uint32_t)p.n_cta_x;
     if (g0 >= g1) {                       // nothing to time: keep the weight, no rate
@@ -536,31 +612,66 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       p.obs_write[3 + 3 * blockIdx.x] = __float_as_uint(1.f);
     }
   }
-  const unsigned int units = (unsigned int)p.batch * p.n_kv_heads;   // (sequence, kv-head) pairs
-
   if (warp == kServiceWarp) {
     // ---------------------------- service warp ---------------------------- //
+    const int n_warps = gridDim.x * gridDim.y, my_warp = blockIdx.y * gridDim.x + blockIdx.x;
+    if (p.pub_n > 0) {
+      // Home GPU: the service warps of the grid share the (sequence, peer) pairs; each
+      // stores one sequence's query rows into one peer's inbox.  All stores of a warp go
+      // out first, then one system fence, then the per-sequence tags.
+      const int row16 = p.n_q_heads * (kHeadDim * 2 / 16);        // 16-byte words per sequence
+      const int n_pairs = p.batch * p.pub_n;
+      for (int pair = my_warp; pair < n_pairs; pair += n_warps) {
+        const int b = pair / p.pub_n, j = pair - b * p.pub_n;
+        const uint4* src = reinterpret_cast<const uint4*>(p.q) + (int64_t)b * row16;
+        uint4* dst = p.pub_q[j] + (int64_t)b * row16;
+        for (int i0 = 0; i0 < row16; i0 += 32 * 8) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * 32 + lane;
+            if (i < row16) v[u] = __ldcg(src + i);
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * 32 + lane;
+            if (i < row16) dst[i] = v[u];
+          }
+        }
+      }
+      if (my_warp < n_pairs) {
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0)
+          for (int pair = my_warp; pair < n_pairs; pair += n_warps) {
+            const int b = pair / p.pub_n, j = pair - b * p.pub_n;
+            st_release_sys_u64(p.pub_tags[j] + b, epoch);
+          }
+        if (lane == 0) trace_first(p, 1);
+      }
+    }
     // Sequences with no token in this shard have no CTA of their own.  Their rows
     // (neutral, or -- on the home GPU -- the merge of the peers' rows) are written by the
     // service warps: unit (empty sequence e, kv-head h) goes to the service warp of CTA
     // (e * heads_here + h) mod gridDim.x, so a ragged batch whose sequences mostly live on
     // other GPUs does not serialise its merge in one warp.
     if (p.fuse) {
-      int n_done = 0, unit = 0;
-      bool peers_ok = true, waited = false;
+      int unit = 0;
       for (int b = 0; b < p.batch; ++b) {
         if (prefix[b + 1] != prefix[b]) continue;
         for (int h = 0; h < heads_here; ++h, ++unit) {
           if (unit % (int)gridDim.x != (int)blockIdx.x) continue;
-          if (p.mg_n > 0 && !waited) { peers_ok = wait_peer_flags(p, lane); waited = true; }
-          if (peers_ok) combine_group<(WPH > 1)>(p, b, (head0 + h) * p.group, p.group, 0, -1, lane);
-          ++n_done;
+          const int qh0 = (head0 + h) * p.group;
+          // a peer's rows land in the home GPU's slot: not before the query of this epoch is
+          // here, which is also when the home GPU has finished reading the previous rows
+          if (p.q_tags && !wait_q_tag(p, epoch, b, lane, abort_flag)) return;
+          bool ok = true;
+          if (p.mg_n > 0) ok = wait_peer_tags(p, epoch, (int64_t)b * p.n_q_heads + qh0, lane);
+          if (ok) {
+            combine_group<(WPH > 1)>(p, b, qh0, p.group, 0, -1, lane);
+            release_unit(p, epoch, b, qh0, p.group, lane);
+          }
         }
-      }
-      if (n_done && p.done_flag) {
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) count_done(p, n_done, units);
       }
     }
     return;
@@ -622,15 +733,8 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
           if (++tpos == p.tiles_per_page) tpos = 0;
           int got = 1;
           if (lane == 0) {
-            got = 0;
-            for (uint32_t w = 0; w < kPollLimit; ++w) {
-              if (mbar_try_wait(empty(ring, stage), ph ^ 1)) { got = 1; break; }
-              if (*abort_flag) break;
-            }
-            if (!got) {
-              atomicOr(p.status, kStPipeTimeout);
-              *abort_flag = 1;
-            }
+            got = pipe_wait(empty(ring, stage), ph ^ 1, abort_flag, pipe_deadline) ? 1 : 0;
+            if (!got) pipe_failed(p, abort_flag);
           }
           got = __shfl_sync(0xffffffffu, got, 0);
           if (!got) { ok = false; break; }
@@ -700,7 +804,6 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
   const uint32_t krow_off = krow * 128, kx = krow & 7;
   const uint32_t vrow_off = vrow * 128, vx = vrow & 7;
 
-  bool q_ready = (p.q_flag == nullptr);
   const bool ps16 = (p.page_size % kTileTok) == 0;
 
   int s = find_seq(prefix, p.batch, g0);
@@ -711,25 +814,10 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
     const int seg_end = min(g1, prefix[s + 1]);
     const int len = p.seq_lens[s];
 
-    if (!q_ready) {
-      // The query of this epoch is pushed by the home GPU; wait for its flag.
-      int okq = 1;
-      if (lane == 0) {
-        uint64_t t0, now;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-        okq = 0;
-        for (;;) {
-          if (ld_acquire_sys_u64(p.q_flag) >= p.q_epoch) { okq = 1; break; }
-          if (*abort_flag) break;
-          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-          if (now - t0 > p.q_timeout_ns) break;
-          __nanosleep(64);
-        }
-        if (!okq) { atomicOr(p.status, kStQTimeout); *abort_flag = 1; }
-      }
-      okq = __shfl_sync(0xffffffffu, okq, 0);
-      if (!okq) return;
-      q_ready = true;
+    // The query rows of this epoch are pushed by the home GPU, sequence by sequence.
+    if (p.q_tags) {
+      if (!wait_q_tag(p, epoch, s, lane, abort_flag)) return;
+      if (warp == 0 && lane == 0) trace_first(p, 1);
     }
 
     // Q^T B-fragments: column n = g is q head kvh*G + g (zero beyond the group).
@@ -795,12 +883,8 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       const uint32_t sk = sbase + stage * L::kSlotBytes + koff;
       const uint32_t sv = sbase + stage * L::kSlotBytes + voff;
 
-      bool got = false;
-      for (uint32_t w = 0; w < kPollLimit; ++w) {
-        if (mbar_try_wait(full(0, stage, hh), ph)) { got = true; break; }
-        if (*abort_flag) break;
-      }
-      if (!got) { if (lane == 0) { atomicOr(p.status, kStPipeTimeout); *abort_flag = 1; } return; }
+      bool got = pipe_wait(full(0, stage, hh), ph, abort_flag, pipe_deadline);
+      if (!got) { if (lane == 0) pipe_failed(p, abort_flag); return; }
 
       float sc[4];
       if (active) {
@@ -822,12 +906,8 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
             mma_16816<false>(sb, a, qf[2 * kp + 1][0], qf[2 * kp + 1][1]);
           }
           // per-token K scales (rows g and g+8 of the score tile)
-          got = false;
-          for (uint32_t w = 0; w < kPollLimit; ++w) {
-            if (mbar_try_wait(scale_full(0, stage), ph)) { got = true; break; }
-            if (*abort_flag) break;
-          }
-          if (!got) { if (lane == 0) { atomicOr(p.status, kStPipeTimeout); *abort_flag = 1; } return; }
+          got = pipe_wait(scale_full(0, stage), ph, abort_flag, pipe_deadline);
+          if (!got) { if (lane == 0) pipe_failed(p, abort_flag); return; }
           const __half* ksc = reinterpret_cast<const __half*>(sgen + L::kScaleOff + stage * L::kScaleSlot);
           const float k0 = __half2float(ksc[g * scale_stride + hh]) * p.scale_log2;
           const float k1 = __half2float(ksc[(g + 8) * scale_stride + hh]) * p.scale_log2;
@@ -875,23 +955,15 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       __syncwarp();
       if (lane == 0) mbar_arrive(empty(0, stage));
 
-      got = false;
-      for (uint32_t w = 0; w < kPollLimit; ++w) {
-        if (mbar_try_wait(full(1, stage, hh), ph)) { got = true; break; }
-        if (*abort_flag) break;
-      }
-      if (!got) { if (lane == 0) { atomicOr(p.status, kStPipeTimeout); *abort_flag = 1; } return; }
+      got = pipe_wait(full(1, stage, hh), ph, abort_flag, pipe_deadline);
+      if (!got) { if (lane == 0) pipe_failed(p, abort_flag); return; }
 
       if (active) {
         if constexpr (kQuant) {
           // fold the per-token V scales into P (tokens g and g+8; 0 past the end so that a
           // garbage scale there cannot poison the sum)
-          bool gots = false;
-          for (uint32_t w = 0; w < kPollLimit; ++w) {
-            if (mbar_try_wait(scale_full(1, stage), ph)) { gots = true; break; }
-            if (*abort_flag) break;
-          }
-          if (!gots) { if (lane == 0) { atomicOr(p.status, kStPipeTimeout); *abort_flag = 1; } return; }
+          const bool gots = pipe_wait(scale_full(1, stage), ph, abort_flag, pipe_deadline);
+          if (!gots) { if (lane == 0) pipe_failed(p, abort_flag); return; }
           const __half* vsc = reinterpret_cast<const __half*>(
               sgen + L::kScaleOff + (NSTAGE + stage) * L::kScaleSlot);
           const float v0 = g < valid ? __half2float(vsc[g * scale_stride + hh]) : 0.f;
@@ -945,12 +1017,12 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
 
     if (gt >= g1 && p.obs_write && warp == 0 && lane == 0 && blockIdx.y == 0) {
       // this CTA's tiles are done: what the next launch's split is computed from
-      unsigned long long t_end;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_end));
+      const unsigned long long t_end = global_ns();
       p.obs_write[1 + 3 * blockIdx.x] = (uint32_t)min(t_end - t_start, 0xffffffffull);
       p.obs_write[2 + 3 * blockIdx.x] = (uint32_t)(g1 - g0);
       p.obs_write[3 + 3 * blockIdx.x] = __float_as_uint(cta_weight[blockIdx.x]);
     }
+    if (gt >= g1 && warp == 0 && lane == 0) trace_max(p, 2);
     // flush this (CTA, sequence) partial
     if (active) {
 #pragma unroll
@@ -1035,93 +1107,12 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
           hi = p.grp_slot0 + g_hi + s;
         }
       }
-      if (last && p.mg_n > 0) last = wait_peer_flags(p, lane) ? 1 : 0;   // home: peers' rows needed
+      if (last && lane == 0) trace_max(p, 3);
+      if (last && p.mg_n > 0)    // home: the peers' rows of this pair are needed
+        last = wait_peer_tags(p, epoch, (int64_t)s * p.n_q_heads + (int64_t)kvh * G, lane) ? 1 : 0;
       if (last) {
         combine_group<(WPH > 1)>(p, s, kvh * G, G, lo, hi, lane);
-        if (p.done_flag) {
-          __threadfence_system();
-          __syncwarp();
-          if (lane == 0) count_done(p, 1u, units);
-        }
-      }
-    }
-  }
-}
-
-// Merge the per-CTA partials of each (sequence, q head) and either write the final
-// output or this shard's (O, lse) partial -- into local memory or, through a P2P
-// mapping, straight into the home GPU's slot.  Replaces attn_combine
-// (PeerKV csrc/peer_attn_kernels.cuh:50-61).
-struct CombineParams {
-  const int32_t* seq_lens;
-  const float* part_o;
-  const float* part_ml;
-  int batch, n_q_heads, page_size, tiles_per_page, n_cta_x;
-  void* out;        // [B][Hq][128] in out_dtype, or null
-  int out_dtype;    // 0 f16, 1 bf16, 4 f32
-  float* o_part;    // [B][Hq][128] f32 normalised, or null
-  float* lse_part;  // [B][Hq] natural log, or null
-  // completion signal (multi-GPU): the last block to finish releases *done_flag = done_epoch
-  unsigned int* done_counter;  // local, zero between launches
-  uint64_t* done_flag;         // may live on another GPU
-  uint64_t done_epoch;
-  const uint32_t* status;      // this shard's status word: no signal after a timed-out wait
-};
-
-
-constexpr int kCombineHeads = 4;  // q heads per combine block (one warp-quad of 128 threads each)
-
-__global__ void __launch_bounds__(128 * kCombineHeads)
-decode_combine_kernel(const CombineParams p) {
-  extern __shared__ int prefix_sm[];
-  build_tile_prefix(prefix_sm, p.seq_lens, p.batch, p.page_size, p.tiles_per_page);
-  const int b = blockIdx.x;
-  const int h = blockIdx.y * kCombineHeads + (threadIdx.x >> 7);
-  const int d = threadIdx.x & 127;
-  if (h < p.n_q_heads) {
-    const int total = prefix_sm[p.batch];
-    const int per = (total + p.n_cta_x - 1) / max(p.n_cta_x, 1);
-    const int t0 = prefix_sm[b], t1 = prefix_sm[b + 1];
-    float m = -INFINITY, l = 0.f, acc = 0.f;
-    if (t1 > t0) {
-      const int c0 = t0 / per, c1 = (t1 - 1) / per;
-      for (int c = c0; c <= c1; ++c) {
-        const int64_t row = (int64_t)(c + b) * p.n_q_heads + h;
-        const float ms = p.part_ml[row * 2], ls = p.part_ml[row * 2 + 1];
-        const float os = p.part_o[row * kHeadDim + d];
-        const float mn = fmaxf(m, ms);
-        const float ca = exp2f(m - mn), cs = exp2f(ms - mn);
-        l = l * ca + ls * cs;
-        acc = acc * ca + os * cs;
-        m = mn;
-      }
-    }
-    const float o = l > 0.f ? acc / l : 0.f;
-    const int64_t idx = ((int64_t)b * p.n_q_heads + h) * kHeadDim + d;
-    if (p.out) store_out(p.out, p.out_dtype, idx, o);
-    if (p.o_part) p.o_part[idx] = o;
-    if (p.lse_part && d == 0)
-      p.lse_part[(int64_t)b * p.n_q_heads + h] =
-          l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
-  }
-  if (p.done_flag) {
-    // Every block publishes its stores system-wide, then counts in; the last one
-    // releases the flag that the home GPU's merge kernel waits on.
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      const unsigned int nblk = gridDim.x * gridDim.y;
-      const unsigned int prev = atomicAdd(p.done_counter, 1u);
-      if (prev == nblk - 1) {
-        *p.done_counter = 0;
-        // A partial computed without its query (or from a stalled pipeline) is not
-        // announced: the home GPU's merge then reports the missing partial itself.
-        const uint32_t bad = *reinterpret_cast<const volatile uint32_t*>(p.status) &
-                             (kStPipeTimeout | kStQTimeout);
-        if (!bad) {
-          __threadfence_system();
-          st_release_sys_u64(p.done_flag, p.done_epoch);
-        }
+        release_unit(p, epoch, s, kvh * G, G, lane);
       }
     }
   }

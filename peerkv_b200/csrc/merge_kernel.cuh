@@ -1,5 +1,5 @@
 // Cross-GPU exchange kernels: q publish (home -> peers, P2P stores), the single-pass
-// N-way LSE merge (with a bounded wait on the peers' epoch flags) and the KV
+// N-way LSE merge (with a bounded wait on the peers' per-row epoch tags) and the KV
 // quantiser.  Replaces merge2_h (PeerKV csrc/peer_attn_kernels.cuh:64-73) and the
 // cudaMemcpyAsync + event fork/join of csrc/peer_fused_attn_ext.cu:100-102,112-128.
 #pragma once
@@ -7,40 +7,43 @@
 
 namespace pkv {
 
-constexpr int kMaxWorld = 16;
-
 struct PublishParams {
-  const uint4* q;          // [n16] 16-byte words of q
-  int64_t n16;
+  const uint4* q;          // [batch][row16] 16-byte words of q
+  int batch, row16;        // sequences; 16-byte words per sequence (Hq * 16)
   uint4* dst[kMaxWorld];   // peers' q inboxes (P2P mapped), one block per peer
-  uint64_t* flag[kMaxWorld];
-  uint64_t epoch;
+  uint64_t* tags[kMaxWorld];   // peers' per-sequence q tags
+  const uint64_t* epoch_base;
+  uint64_t epoch_rel;
 };
 
-// One 1024-thread block per destination peer: all loads first, then the P2P stores,
-// one block barrier, and a single system-scope release of that peer's q flag (the
-// barrier makes the release cumulative over the whole block's stores).
+// The stand-alone q publish (the fused home step does the same in its own prologue).
+// One 1024-thread block per destination peer: all loads first, then the P2P stores, a
+// system fence per thread, one block barrier, and the per-sequence tags.
 __global__ void __launch_bounds__(1024) publish_q_kernel(const PublishParams p) {
   uint4* dst = p.dst[blockIdx.x];
-  for (int64_t i0 = 0; i0 < p.n16; i0 += 4096) {
+  const int64_t n16 = (int64_t)p.batch * p.row16;
+  for (int64_t i0 = 0; i0 < n16; i0 += 4096) {
     uint4 v[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int64_t i = i0 + threadIdx.x + 1024 * u;
-      if (i < p.n16) v[u] = __ldcg(p.q + i);
+      if (i < n16) v[u] = __ldcg(p.q + i);
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int64_t i = i0 + threadIdx.x + 1024 * u;
-      if (i < p.n16) dst[i] = v[u];
+      if (i < n16) dst[i] = v[u];
     }
   }
+  __threadfence_system();
   __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    st_release_sys_u64(p.flag[blockIdx.x], p.epoch);
-  }
+  const uint64_t epoch = (p.epoch_base ? *reinterpret_cast<const volatile uint64_t*>(p.epoch_base) : 0ull) +
+                         p.epoch_rel;
+  for (int b = threadIdx.x; b < p.batch; b += blockDim.x) st_release_sys_u64(p.tags[blockIdx.x] + b, epoch);
 }
+
+// Adds `step` to a device-resident epoch base: the last node of a captured decode step.
+__global__ void bump_epoch_kernel(uint64_t* base, uint64_t step) { *base += step; }
 
 struct MergeParams {
   const float* o_parts;     // part i at o_parts + i*o_stride: [rows][128]
@@ -50,40 +53,44 @@ struct MergeParams {
   void* out;
   int out_dtype;
   float* lse_out;
-  // optional bounded wait: flags[i] >= epoch for every i with bit i of wait_mask
-  const uint64_t* flags;
+  // optional bounded wait, per row: tags[i*tag_stride + row] >= epoch for every part i with
+  // bit i of wait_mask
+  const uint64_t* tags;
+  int64_t tag_stride;
   uint32_t wait_mask;
-  uint64_t epoch;
+  const uint64_t* epoch_base;
+  uint64_t epoch_rel;
   uint64_t timeout_ns;
   uint32_t* status;
 };
 
 // One warp per (sequence, q head) row; each lane owns 4 of the 128 output dims.
 __global__ void __launch_bounds__(256) merge_partials_kernel(const MergeParams p) {
-  __shared__ int s_ok;
-  if (p.flags && p.wait_mask) {
-    if (threadIdx.x == 0) s_ok = 1;
-    __syncthreads();
-    if (threadIdx.x < p.n_parts && ((p.wait_mask >> threadIdx.x) & 1u)) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= p.rows) return;
+  if (p.tags && p.wait_mask) {
+    const uint64_t epoch = (p.epoch_base ? *reinterpret_cast<const volatile uint64_t*>(p.epoch_base) : 0ull) +
+                           p.epoch_rel;
+    bool ok = true;
+    if (lane < p.n_parts && ((p.wait_mask >> lane) & 1u)) {
+      const uint64_t* tag = p.tags + lane * p.tag_stride + row;
       uint64_t t0, now;
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
       for (;;) {
-        if (ld_acquire_sys_u64(p.flags + threadIdx.x) >= p.epoch) break;
+        if (ld_acquire_sys_u64(tag) >= epoch) break;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-        if (now - t0 > p.timeout_ns) {
+        if ((*reinterpret_cast<const volatile uint32_t*>(p.status) & kStPartialTimeout) ||
+            now - t0 > p.timeout_ns) {
           atomicOr(p.status, kStPartialTimeout);
-          s_ok = 0;
+          ok = false;
           break;
         }
         __nanosleep(32);
       }
     }
-    __syncthreads();
-    if (!s_ok) return;   // status says why; the output is left untouched
+    if (!__all_sync(0xffffffffu, ok)) return;   // status says why; the row is left untouched
   }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (row >= p.rows) return;
   float L = -INFINITY;
   for (int i = 0; i < p.n_parts; ++i) L = fmaxf(L, __ldcg(p.lse_parts + i * p.lse_stride + row));
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -102,17 +109,7 @@ __global__ void __launch_bounds__(256) merge_partials_kernel(const MergeParams p
     acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
   }
   const int64_t idx = (int64_t)row * kHeadDim + lane * 4;
-  if (p.out_dtype == 4) {
-    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + idx) = acc;
-  } else if (p.out_dtype == 1) {
-    __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y), b = __floats2bfloat162_rn(acc.z, acc.w);
-    uint2 v = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
-    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + idx) = v;
-  } else {
-    __half2 a = __floats2half2_rn(acc.x, acc.y), b = __floats2half2_rn(acc.z, acc.w);
-    uint2 v = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
-    *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + idx) = v;
-  }
+  store_out4(p.out, p.out_dtype, idx, acc);
   if (p.lse_out && lane == 0) p.lse_out[row] = L > -INFINITY ? L + __logf(wsum) : -INFINITY;
 }
 

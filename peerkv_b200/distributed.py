@@ -63,6 +63,13 @@ class DistPeerGroup:
     def status(self) -> int:
         return self.shard.status() | self.xchg.status()
 
+    def resync(self):
+        """After an error on any rank: all ranks agree on the largest epoch reached, so the
+        next step's tags mean the same thing everywhere (a collective; call it on every rank)."""
+        t = torch.tensor([self.xchg.epoch()], dtype=torch.int64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.pg)
+        self.xchg.resync(int(t.item()))
+
     def close(self):
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.pg)

@@ -60,6 +60,10 @@ class Exchange:
         check(_lib.lib().pkv_exchange_epoch(self._h, C.byref(v)))
         return int(v.value)
 
+    def resync(self, epoch: int):
+        """Sets the epoch (every rank passes the same value) after a failed or skipped step."""
+        check(_lib.lib().pkv_exchange_resync(self._h, int(epoch)))
+
     def close(self):
         if getattr(self, "_h", None):
             _lib.lib().pkv_exchange_destroy(self._h)
@@ -131,6 +135,8 @@ class PeerGroup:
         scale = 1.0 / math.sqrt(D) if scale is None else scale
         if len(shards) != self.world:
             raise PeerKVError("one (K, V) per GPU of the group is required")
+        if q.device != self.devices[0]:
+            raise PeerKVError(f"q lives on {q.device}, the group's home GPU is {self.devices[0]}")
         args = []
         for r, (K, V) in enumerate(shards):
             if K.device != self.devices[r]:
@@ -150,10 +156,15 @@ class PeerGroup:
         B, Hq, D = q.shape
         scale = 1.0 / math.sqrt(D) if scale is None else scale
         args = []
+        if q.device != self.devices[0]:
+            raise PeerKVError(f"q lives on {q.device}, the group's home GPU is {self.devices[0]}")
         for r in range(self.world):
             kp, vp = pools[r]
-            args.append(ops.make_args(q, ops.paged_view(kp, vp), tables[r], tables[r].stride(0),
-                                      lens[r], scale))
+            d = self.devices[r]
+            ops._same_gpu(kp, d, f"pool {r}"); ops._same_gpu(vp, d, f"pool {r}")
+            tab, ln = ops._meta(tables[r], d, "block table"), ops._meta(lens[r], d, "shard lengths")
+            args.append(ops.make_args(q, ops.paged_view(kp, vp), tab, tab.stride(0), ln, scale))
+            args[-1]._keep = (tab, ln)
         out = torch.empty_like(q) if out is None else out
         return self._step(q, args, out, after_event)
 
@@ -164,14 +175,13 @@ class PeerGroup:
         bases=None means round robin (id mod N)."""
         B, W = block_table.shape
         self._ensure_tables(W)
-        bt = block_table if block_table.dtype == torch.int32 else block_table.to(torch.int32)
-        sl = seq_lens if seq_lens.dtype == torch.int32 else seq_lens.to(torch.int32)
+        home = self.devices[0]
+        bt, sl = ops._meta(block_table, home, "block_table"), ops._meta(seq_lens, home, "seq_lens")
         n = self.world
         tabs = (C.c_void_p * n)(*[t.data_ptr() for t in self._tables])
         lens = (C.c_void_p * n)(*[t.data_ptr() for t in self._lens])
         mode = 1 if bases is None else 0
         b = (C.c_int64 * n)(*([0] * n if bases is None else list(bases)))
-        home = self.devices[0]
         check(_lib.lib().pkv_split_block_table(home.index, bt.data_ptr(), bt.stride(0), sl.data_ptr(),
                                                B, page_size, n, mode, b, tabs, self._max_pages, lens,
                                                ops._stream(home)))

@@ -143,6 +143,27 @@ def contiguous_view(K: torch.Tensor, V: torch.Tensor) -> KvView:
     return v
 
 
+def _meta(t: torch.Tensor, device: torch.device, name: str) -> torch.Tensor:
+    """Block tables and lengths as the kernels need them: int32, on `device`, rows
+    contiguous.  The reference accepts host-side metadata (it calls .item() on it), so a
+    CPU tensor or one on another GPU is moved here rather than refused; a pointer that is
+    not valid on `device` must never reach a kernel."""
+    if not isinstance(t, torch.Tensor):
+        t = torch.as_tensor(t)
+    if t.dtype != torch.int32:
+        t = t.to(torch.int32)
+    if t.device != device:
+        t = t.to(device, non_blocking=True)
+    if t.dim() > 0 and t.stride(-1) != 1:
+        t = t.contiguous()
+    return t
+
+
+def _same_gpu(t: torch.Tensor, device: torch.device, name: str):
+    if t is not None and t.device != device:
+        raise PeerKVError(f"{name} lives on {t.device}, expected {device}")
+
+
 def _check_q(q: torch.Tensor):
     _require_cuda(q, "q")
     if q.dim() != 3 or q.shape[2] != HEAD_DIM:
@@ -161,10 +182,11 @@ def decode_paged(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     B, Hq, D = q.shape
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     shard = shard or get_shard(q.device, B, Hq)
-    bt = block_table if block_table.dtype == torch.int32 else block_table.to(torch.int32)
-    sl = seq_lens if seq_lens.dtype == torch.int32 else seq_lens.to(torch.int32)
-    if bt.stride(-1) != 1:
-        bt = bt.contiguous()
+    bt, sl = _meta(block_table, q.device, "block_table"), _meta(seq_lens, q.device, "seq_lens")
+    for t, n in ((k_pool, "k_pool"), (v_pool, "v_pool"), (k_scale, "k_scale"), (v_scale, "v_scale")):
+        _same_gpu(t, q.device, n)
+    if shard.device != q.device:
+        raise PeerKVError(f"the shard context is on {shard.device}, q on {q.device}")
     view = paged_view(k_pool, v_pool, k_scale, v_scale)
     a = make_args(q, view, bt, bt.stride(0), sl, scale)
     if out is None:
@@ -182,10 +204,11 @@ def partial_paged(q, k_pool, v_pool, block_table, seq_lens, scale=None, k_scale=
     B, Hq, D = q.shape
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     shard = shard or get_shard(q.device, B, Hq)
-    bt = block_table if block_table.dtype == torch.int32 else block_table.to(torch.int32)
-    sl = seq_lens if seq_lens.dtype == torch.int32 else seq_lens.to(torch.int32)
-    if bt.stride(-1) != 1:
-        bt = bt.contiguous()
+    bt, sl = _meta(block_table, q.device, "block_table"), _meta(seq_lens, q.device, "seq_lens")
+    for t, n in ((k_pool, "k_pool"), (v_pool, "v_pool"), (k_scale, "k_scale"), (v_scale, "v_scale")):
+        _same_gpu(t, q.device, n)
+    if shard.device != q.device:
+        raise PeerKVError(f"the shard context is on {shard.device}, q on {q.device}")
     view = paged_view(k_pool, v_pool, k_scale, v_scale)
     a = make_args(q, view, bt, bt.stride(0), sl, scale)
     if o_part is None:
@@ -200,6 +223,7 @@ def partial_contiguous(q, K, V, scale=None, shard: Optional[Shard] = None, o_par
     """One shard's partial from contiguous K/V [B, Hkv, T, D]; q [B, Hq, D]."""
     q = _check_q(q)
     _require_cuda(K, "K")
+    _same_gpu(K, q.device, "K"); _same_gpu(V, q.device, "V")
     B, Hq, D = q.shape
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     shard = shard or get_shard(q.device, B, Hq)
@@ -219,6 +243,7 @@ def decode_contiguous(q, K, V, scale=None, out=None, shard: Optional[Shard] = No
     """Whole attention over contiguous K/V [B, Hkv, T, D] on one GPU -> [B, Hq, D]."""
     q = _check_q(q)
     _require_cuda(K, "K")
+    _same_gpu(K, q.device, "K"); _same_gpu(V, q.device, "V")
     B, Hq, D = q.shape
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     shard = shard or get_shard(q.device, B, Hq)

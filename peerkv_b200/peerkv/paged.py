@@ -93,8 +93,7 @@ def _same_device(query, caches, block_table, seq_lens, bases, bs, scale):
     n = len(caches)
     B, W = block_table.shape
     dev = query.device
-    bt = block_table.to(torch.int32)
-    sl = seq_lens.to(torch.int32)
+    bt, sl = ops._meta(block_table, dev, "block_table"), ops._meta(seq_lens, dev, "seq_lens")
     tabs = [torch.zeros(B, W, dtype=torch.int32, device=dev) for _ in range(n)]
     lens = [torch.zeros(B, dtype=torch.int32, device=dev) for _ in range(n)]
     _lib.check(_lib.lib().pkv_split_block_table(

@@ -200,6 +200,42 @@ def enforce_do_no_harm(point: OperatingPoint, kv_bytes: int, local_free_bytes: i
     return point
 
 
+def capacity_spill_split(pages_per_seq: Sequence[int], seq_lens: Sequence[int], page_size: int,
+                         caps: Sequence[float]):
+    """Capacity-limited placement of a batch's pages (the ragged benchmark configuration).
+
+    The pages of all sequences form one list, sequence after sequence.  GPU g takes up to
+    floor(caps[g] * total / N) of them in order; what is left spills to the next GPU and
+    the last GPU takes the rest.  Pools are compact: a page's local id is its arrival order
+    on its GPU.  Returns (tables [N, B, W] int32 local ids, tokens [N, B] int64, pages used
+    per GPU [N]); only a sequence's last page can be partial and it stays last in its
+    owner's list."""
+    import numpy as np
+    n = len(caps)
+    pages = np.asarray(pages_per_seq, dtype=np.int64)
+    lens = np.asarray(seq_lens, dtype=np.int64)
+    B, total = len(pages), int(pages.sum())
+    quota = [int(c * total / n) for c in caps]
+    quota[-1] = total
+    hi = np.minimum(np.cumsum(quota), total)          # GPU g owns flat pages [lo[g], hi[g])
+    hi[-1] = total
+    lo = np.concatenate([[0], hi[:-1]])
+    W = int(pages.max()) if B else 1
+    tab = np.zeros((n, B, max(W, 1)), dtype=np.int32)
+    tok = np.zeros((n, B), dtype=np.int64)
+    start = np.concatenate([[0], np.cumsum(pages)])
+    for i in range(B):
+        p0, p1 = int(start[i]), int(start[i + 1])
+        for g in range(n):
+            a, b = max(p0, int(lo[g])), min(p1, int(hi[g]))
+            if a >= b:
+                continue
+            tab[g, i, :b - a] = np.arange(a - lo[g], b - lo[g], dtype=np.int32)
+            tok[g, i] = (b - a) * page_size - ((p1 * page_size - (start[i] * page_size + lens[i])) if b == p1 else 0)
+    used = (hi - lo).astype(np.int64)
+    return tab, tok, used
+
+
 class PagePlacer:
     """Allocation-time page -> (gpu, local id) decisions for a sharded KV pool.
 

@@ -107,7 +107,9 @@ def test_query_that_never_arrives_is_a_status_bit_not_a_hang():
     from peerkv_b200 import _lib, ops
     from peerkv_b200.group import Exchange
     dev0, dev1 = torch.device("cuda:0"), torch.device("cuda:1")
-    B, Hq, Hkv, D, T = 1, 32, 8, 128, 64
+    # long enough that every CTA has more tiles than ring slots: the producers fill their
+    # rings and then block on the consumers, which are waiting for the query
+    B, Hq, Hkv, D, T = 1, 32, 8, 128, 16 * 8 * 160
     x0, x1 = Exchange(dev0, 0, 2, B, Hq), Exchange(dev1, 1, 2, B, Hq)
     x0.attach(x1); x1.attach(x0)
     shard = ops.Shard(dev1, B, Hq)
@@ -119,7 +121,7 @@ def test_query_that_never_arrives_is_a_status_bit_not_a_hang():
     with torch.cuda.device(dev1):
         _lib.check(_lib.lib().pkv_peer_step(x1._h, shard._h, C.byref(a), 0, 0, ops._stream(dev1)))
         torch.cuda.synchronize(dev1)
-        assert shard.status() & _lib.ST_Q_TIMEOUT
+        assert shard.status() == _lib.ST_Q_TIMEOUT      # that bit and no other (no pipeline time-out)
         # the GPU still works: an ordinary decode on the same shard object
         out = ops.decode_contiguous(q, K, V, shard=shard)
         ref = orc.dense_attention_fp32(q.cpu().unsqueeze(2), K.cpu(), V.cpu()).squeeze(2)
@@ -132,6 +134,71 @@ def test_query_that_never_arrives_is_a_status_bit_not_a_hang():
                                              ops._stream(dev0)))
         torch.cuda.synchronize(dev0)
         assert x0.status() & _lib.ST_PARTIAL_TIMEOUT
+    x0.close(); x1.close(); shard.close()
+
+
+def test_back_to_back_steps_with_a_sequence_that_leaves_the_peer():
+    """Two steps enqueued with no synchronisation in between.  In the first, sequence 1
+    has tokens on the peer GPU; in the second it has none there (its rows from the peer
+    become the neutral ones).  The peer's second kernel starts while the home GPU may
+    still be merging the first step: nothing of the second step may land in the home
+    GPU's slot before the home GPU has finished reading the first."""
+    from peerkv_b200.group import PeerGroup
+    devs = [torch.device("cuda:0"), torch.device("cuda:1")]
+    bs, Hq, Hkv, D = 16, 32, 8, 128
+    g = torch.Generator().manual_seed(9)
+    n_pages = 4096
+    pools_cpu = [torch.randn(2, n_pages, bs, Hkv, D, generator=g).bfloat16() for _ in devs]
+    B = 3
+    q = torch.randn(B, Hq, D, generator=g).bfloat16()
+    # per GPU: local block tables; GPU 0 holds a long shard so that its merge comes late
+    tab = [torch.arange(B * 1024, dtype=torch.int32).view(B, 1024) for _ in devs]
+    lens1 = [torch.tensor([16000, 16000, 16000], dtype=torch.int32), torch.tensor([800, 4000, 16], dtype=torch.int32)]
+    lens2 = [torch.tensor([16000, 16000, 16000], dtype=torch.int32), torch.tensor([800, 0, 16], dtype=torch.int32)]
+    grp = PeerGroup(devs, B, Hq)
+    pools = [(p[0].to(d), p[1].to(d)) for p, d in zip(pools_cpu, devs)]
+    tabs = [t.to(d) for t, d in zip(tab, devs)]
+    l1 = [t.to(d) for t, d in zip(lens1, devs)]
+    l2 = [t.to(d) for t, d in zip(lens2, devs)]
+    qd = q.to(devs[0])
+    out1, out2 = torch.empty_like(qd), torch.empty_like(qd)
+    for d in devs:
+        torch.cuda.synchronize(d)
+    for rep in range(20):                         # the window is narrow: many tries
+        grp.decode_paged_local(qd, pools, tabs, l1, out=out1)
+        grp.decode_paged_local(qd, pools, tabs, l2, out=out2)
+    for d in devs:
+        torch.cuda.synchronize(d)
+
+    def want(lens):
+        parts = [orc.paged_partial_oracle(q, pools_cpu[r], tab[r], lens[r]) for r in range(2)]
+        return orc.merge_n([p[0] for p in parts], [p[1] for p in parts])[0]
+    assert close(out1, want(lens1))
+    assert close(out2, want(lens2))
+    grp.raise_on_status()
+
+
+def test_a_rejected_step_leaves_the_epoch_where_it_was():
+    import ctypes as C
+    from peerkv_b200 import _lib, ops
+    from peerkv_b200.group import Exchange
+    dev0, dev1 = torch.device("cuda:0"), torch.device("cuda:1")
+    B, Hq, Hkv, D, T = 2, 32, 8, 128, 64
+    x0, x1 = Exchange(dev0, 0, 2, B, Hq), Exchange(dev1, 1, 2, B, Hq)
+    x0.attach(x1); x1.attach(x0)
+    shard = ops.Shard(dev1, B, Hq)
+    K = torch.randn(B, Hkv, T, D, device=dev1).half()
+    q = torch.randn(B, Hq, D, device=dev1).half()
+    sl = torch.full((B,), T, dtype=torch.int32, device=dev1)
+    a = ops.make_args(q, ops.contiguous_view(K, K), None, 1, sl, 0.1)
+    a.kv.head_dim = 64                                   # refused by the argument check
+    with torch.cuda.device(dev1):
+        rc = _lib.lib().pkv_peer_step(x1._h, shard._h, C.byref(a), 0, 0, ops._stream(dev1))
+    assert rc == -3 and x1.epoch() == 0
+    x1.resync(5)
+    assert x1.epoch() == 5
+    with pytest.raises(_lib.PeerKVError):
+        x1.resync(4)
     x0.close(); x1.close(); shard.close()
 
 

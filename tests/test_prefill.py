@@ -3,9 +3,7 @@ umallm/peer_parallel_attn.py:112-140 and tests/test_peer_parallel.py:63-95).
 
 CPU: the host-side construction (one "sequence" per query row, causality by length) is
 checked against dense causal attention with the CPU oracle standing in for the one
-library call.  GPU: the same entry points on the real kernels; these two were written
-after this build's GPU time had run out, so their first run on a GPU decides them
-(non-strict xfail: a failure is reported, not fatal to the rest of the suite)."""
+library call.  GPU: the same entry points on the real kernels."""
 import pytest
 import torch
 import torch.nn.functional as F
@@ -60,7 +58,6 @@ def test_multi_query_host_logic(oracle_backed):
 
 
 @pytest.mark.gpu
-@pytest.mark.xfail(strict=False, reason="first GPU run of this test: written after the GPU time ran out")
 def test_ring_prefill_on_gpu():
     from peerkv_b200.peer_parallel_attn import ring_prefill_attention
     dev = torch.device("cuda", 0)
@@ -79,7 +76,6 @@ def test_ring_prefill_on_gpu():
 
 
 @pytest.mark.gpu
-@pytest.mark.xfail(strict=False, reason="first GPU run of this test: written after the GPU time ran out")
 def test_multi_query_partial_on_gpu():
     from peerkv_b200.peer_parallel_attn import flash_partial, peer_parallel_attention
     dev = torch.device("cuda", 0)
