@@ -423,8 +423,7 @@ def parity_check(wl, q, out, N, rank, dev, n_seqs=2):
 def run_llama_step(args):
     import torch
     import torch.distributed as dist
-    from peerkv_b200 import _lib, ops
-    from peerkv_b200.decoder import DecodeStep, LlamaGeometry, ModelWeights, ShardedKVLayer, make_args
+    from peerkv_b200.decoder import DecodeStep, LlamaGeometry, ModelWeights, ShardedKVLayer
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -437,10 +436,17 @@ def run_llama_step(args):
     if N > 1:
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
+    t_setup = time.perf_counter()
+
+    def note(msg):
+        if rank == 0:
+            print(f"[llama-step +{time.perf_counter() - t_setup:6.1f}s] {msg}", file=sys.stderr, flush=True)
+
     HKV = WORKLOADS["long-bf16"]["HKV"]
     g = LlamaGeometry(n_layers=args.layers)
     ctx = args.context or 1048576
     wl = build_workload("long-bf16", ctx, N, rank, dev)
+    note("placement and layer 0's KV built")
     B, HQ = wl["B"], wl["HQ"]
     base, tab, lens = wl["pool"], wl["tab"], wl["len"]
     append = None
@@ -455,50 +461,26 @@ def run_llama_step(args):
         assert bool(full.all()), "the bench context puts whole pages on every GPU"
         lens = lens + 1
         append = (torch.arange(n0, n0 + B, device=dev), torch.zeros(B, dtype=torch.int64, device=dev))
-    layers = [ShardedKVLayer(base if li == 0 else base.clone(), tab, lens) for li in range(g.n_layers)]
-    qbuf = torch.zeros(B, HQ, D, dtype=torch.bfloat16, device=dev)
-    L = _lib.lib()
-    st = ops._stream(dev)
-    scale = 1.0 / math.sqrt(D)
-    largs = [make_args(qbuf, l, scale) for l in layers]
-    if N == 1:
-        shard = ops.Shard(dev, B, HQ)
-        grp = None
-
-        def attend(li, q, out):
-            qbuf.copy_(q)
-            _lib.check(L.pkv_decode(shard._h, C.byref(largs[li]), out.data_ptr(), _lib.PKV_BF16, None, st))
-    else:
+    wl["pool"] = None
+    # every layer has its own KV of the same shape; the values of layers 1.. are copies of
+    # layer 0's N(0,1) pool (the step's time does not depend on them)
+    layers = []
+    for li in range(g.n_layers):
+        pool = base if li == 0 else torch.empty_like(base).copy_(base)
+        layers.append(ShardedKVLayer(pool, tab, lens))
+    note(f"{g.n_layers} layers of KV resident ({base.numel() * 2 * g.n_layers / 2**30:.1f} GiB on this GPU)")
+    grp = None
+    if N > 1:
         from peerkv_b200.distributed import DistPeerGroup
         grp = DistPeerGroup(dev, B, HQ, home=0)
-        shard = grp.shard
-
-        def attend(li, q, out):
-            qbuf.copy_(q)
-            grp.step(largs[li], q=qbuf, out=out)
-
     weights = ModelWeights(g, dev) if rank == 0 else None
-    step = DecodeStep(g, weights, layers, attend, append)
-    if rank == 0 and not args.no_graphs:
-        step.capture(B)
+    note("weights built")
+    step = DecodeStep(g, weights, layers, B, dev, group=grp, append_slots=append)
     tokens = torch.randint(0, g.vocab, (B,), device=dev)
     positions = torch.full((B,), ctx, device=dev, dtype=torch.int64)
-    attn_out = torch.empty(B, HQ, D, dtype=torch.bfloat16, device=dev)
 
     def one_token():
-        if rank == 0:
-            step.home_step(tokens, positions)
-        else:
-            for li in range(g.n_layers):
-                grp.step(largs[li])
-
-    def attention_only():
-        if rank == 0:
-            for li in range(g.n_layers):
-                attend(li, qbuf, attn_out)
-        else:
-            for li in range(g.n_layers):
-                grp.step(largs[li])
+        step.step(tokens, positions)
 
     def timed(fn, n):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -518,32 +500,49 @@ def run_llama_step(args):
             ms = float(t)
         return ms / n
 
-    for _ in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 3)
+    for _ in range(2):
+        one_token()
+    eager_logits = step.logits.float().clone() if rank == 0 else None
+    eager = timed(one_token, max(2, args.steps // 4))
+    note(f"eager step {eager:.3f} ms")
+    if not args.no_graphs:
+        step.capture()
+        note("whole step captured as one graph per GPU")
+    for _ in range(warm):
         one_token()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
     tpot = timed(one_token, args.steps)
-    attn = timed(attention_only, args.steps)
+    attn = timed(step.attention_only, args.steps)
     clocks = sampler.stop() if sampler else None
-    status = shard.status() | (grp.xchg.status() if grp else 0)
+    status = step.shard.status() | (grp.xchg.status() if grp else 0)
     if rank == 0:
+        logit_diff = float((step.logits.float() - eager_logits).abs().max())
         peak, kind = measured_peak()
         kv_bytes = wl["total_tokens"] * wl["bytes_per_token"] * g.n_layers
-        floor_ms = (kv_bytes / N + weights.bytes() - weights.embed.numel() * 2) / (peak * 1e9) * 1e3
+        w_bytes = weights.bytes() - weights.embed.numel() * 2          # the embedding is gathered, not read
+        floor_ms = (kv_bytes / N + w_bytes) / (peak * 1e9) * 1e3
+        rest = tpot - attn
         print(json.dumps({
             "metric": "tpot_ms", "value": tpot, "unit": "ms", "n_gpus": N, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": tpot, "higher_is_better": False, "scaling": "strong",
+            "warmup": warm, "ms_per_step": tpot, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"llama-step: random-init Llama-3-8B architecture ({g.n_layers} layers, hidden "
                                    f"{g.hidden}, {g.n_q_heads}/{g.n_kv_heads} heads, FFN {g.ffn}, vocab {g.vocab}), "
                                    f"batch {B}, {ctx}-token KV per sequence, pages round-robin over {N} GPU(s), "
-                                   "attention on the sharded path, the rest on GPU 0 with torch ops" + ("" if args.no_graphs else " replayed as CUDA graphs"),
+                                   "attention on the sharded path, the rest on GPU 0 (library GEMMs + this library's "
+                                   "rmsnorm / rope+append / swiglu kernels)"
+                                   + ("" if args.no_graphs else ", the whole step one CUDA graph per GPU"),
                        "kv_bytes_per_token_step": kv_bytes, "weight_bytes": weights.bytes()},
             "attention_ms_per_token": attn, "attention_us_per_layer": attn / g.n_layers * 1e3,
-            "rest_ms_per_token": tpot - attn,
-            "hbm_floor_ms": floor_ms, "frac_of_floor": floor_ms / tpot, "peak_kind": kind,
-            "gpu_launches": args.steps * g.n_layers * (1 if N == 1 else N + 1),
+            "rest_ms_per_token": rest, "rest_floor_ms": w_bytes / (peak * 1e9) * 1e3,
+            "rest_over_floor": rest / (w_bytes / (peak * 1e9) * 1e3),
+            "eager_ms_per_token": eager,
+            "hbm_floor_ms": floor_ms, "tpot_over_floor": tpot / floor_ms, "peak_kind": kind,
+            "graph_vs_eager_max_abs_logit_diff": logit_diff,
+            "gpu_launches": args.steps * g.n_layers * (N + 3),
             "clocks": clocks, "device_status": status}), flush=True)
     if grp:
         grp.close()

@@ -286,6 +286,34 @@ int pkv_home_partial(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, vo
 int pkv_home_merge(pkv_exchange* x, int32_t batch, uint32_t wait_mask, void* out,
                    int32_t out_dtype, float* lse_out, void* stream);
 
+/* ---- the rest of a decoder layer (the full-step configuration) ------------- */
+
+/* The small kernels around the attention call of one decoder layer, for a decode batch
+ * of `rows` tokens; the projections in between stay library GEMMs, as in the reference
+ * (csrc/peer_fused_decoder.cu:100-109).  dtype PKV_F16 or PKV_BF16 throughout.
+ *
+ * pkv_add_rmsnorm: if delta != NULL, x += delta in place (the residual add); then
+ *   out = x * rsqrt(mean(x^2) + eps) * weight.  x, delta, out [rows, hidden], weight
+ *   [hidden]; hidden a multiple of 8.  Replaces add_kernel + rmsnorm_kernel
+ *   (csrc/peer_fused_decoder.cu:51-71, 87-95).
+ * pkv_rope_append: qkv [batch, (n_q_heads + 2 n_kv_heads) * head_dim] (q heads, k heads,
+ *   v heads); rotate-half RoPE at angle positions[b] * inv_freq[i] on q and k; q goes to
+ *   q_out [batch, n_q_heads, head_dim]; the rotated k and v are stored into the pools at
+ *   page pages[b], token slot slots[b] (element strides as in pkv_kv_view); pools NULL =
+ *   no append.  No counterpart in the reference (its layer has neither RoPE nor an
+ *   append, :205-206).
+ * pkv_swiglu: out[r, f] = silu(gate_up[r, f]) * gate_up[r, ffn + f]; ffn a multiple of 8.
+ *   Replaces swiglu_kernel (:73-85). */
+int pkv_add_rmsnorm(int device, void* x, const void* delta, const void* weight, void* out,
+                    int32_t rows, int32_t hidden, float eps, int32_t dtype, void* stream);
+int pkv_rope_append(int device, const void* qkv, const int64_t* positions, const float* inv_freq,
+                    int32_t batch, int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim,
+                    void* q_out, void* k_pool, void* v_pool, int64_t page_stride,
+                    int64_t token_stride, int64_t head_stride, const int64_t* pages,
+                    const int64_t* slots, int32_t dtype, void* stream);
+int pkv_swiglu(int device, const void* gate_up, void* out, int32_t rows, int32_t ffn,
+               int32_t dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

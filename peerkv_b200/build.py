@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libpeerkv.so")
 SOURCES = ["api.cu"]
-HEADERS = ["ptx.cuh", "decode_kernel.cuh", "merge_kernel.cuh", os.path.join("..", "..", "include", "peerkv.h")]
+HEADERS = ["ptx.cuh", "decode_kernel.cuh", "merge_kernel.cuh", "layer_kernels.cuh", os.path.join("..", "..", "include", "peerkv.h")]
 
 
 def _nvcc() -> str:
@@ -26,16 +26,32 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found; set NVCC or put it on PATH")
 
 
+def _source_hash() -> str:
+    import hashlib
+    h = hashlib.sha256()
+    for f in SOURCES + HEADERS:
+        path = os.path.join(CSRC, f)
+        h.update(f.encode())
+        if os.path.exists(path):
+            with open(path, "rb") as fh:
+                h.update(fh.read())
+    return h.hexdigest()
+
+
+STAMP = LIB + ".srchash"
+
+
 def _stale() -> bool:
-    if not os.path.exists(LIB):
+    """The library is rebuilt unless it was built from exactly these sources (a content
+    hash kept beside it; file times do not survive a copy of the tree)."""
+    if not os.path.exists(LIB) or not os.path.exists(STAMP):
         return True
-    t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS]
-    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in deps)
+    with open(STAMP) as f:
+        return f.read().strip() != _source_hash()
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile if the library is missing or older than its sources; returns its path."""
+    """Compile if the library is missing or was built from other sources; returns its path."""
     if not force and not _stale():
         return LIB
     cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -44,6 +60,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    with open(STAMP, "w") as f:
+        f.write(_source_hash() + "\n")
     if verbose:
         print(res.stderr)
     return LIB

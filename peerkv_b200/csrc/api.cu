@@ -13,6 +13,7 @@
 
 #include "../../include/peerkv.h"
 #include "merge_kernel.cuh"
+#include "layer_kernels.cuh"
 
 namespace {
 
@@ -70,6 +71,7 @@ struct MapKey {
   int64_t n_pages, page_stride, token_stride, head_stride;
   bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
 };
+constexpr size_t kMapCache = 256;   // tensor maps kept per shard: two per layer of a model and pool
 struct MapEntry {
   MapKey key;
   CUtensorMap map;
@@ -191,7 +193,7 @@ int build_map(pkv_shard* s, const void* base, const pkv_kv_view& kv, CUtensorMap
   *out = e.map;
   if (!s->cache_maps) return PKV_OK;   // encoding is host arithmetic only; nothing is stored
   e.stamp = ++s->stamp;
-  if (s->maps.size() < 32) {
+  if (s->maps.size() < kMapCache) {
     s->maps.push_back(e);
   } else {
     size_t victim = 0;
@@ -341,6 +343,7 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   p.seq_counter = s->counters + 64;
   p.grp_counter = s->counters + s->grp_counter_off;
   p.grp_slot0 = s->grp_slot0;
+  p.sib_slot0 = s->grp_slot0 / pkv::kMaxWph;
   if (s->obs[0] && n_cta_x <= pkv::kMaxCtas) {
     p.obs_read = s->obs[s->obs_parity];
     p.obs_write = s->obs[s->obs_parity ^ 1];
@@ -439,7 +442,7 @@ int pkv_shard_create(pkv_shard** out, int device, int max_batch, int n_q_heads) 
   s->n_q_heads = n_q_heads;
   s->grp_slot0 = (sms + max_batch) * pkv::kMaxWph;                 // per-CTA slots, then per-group slots
   s->n_slots = s->grp_slot0 + (sms + pkv::kGroupCtas - 1) / pkv::kGroupCtas + max_batch;
-  s->maps.reserve(32);
+  s->maps.reserve(kMapCache);
   const size_t o_bytes = (size_t)s->n_slots * n_q_heads * pkv::kHeadDim * sizeof(float);
   const size_t ml_bytes = (size_t)s->n_slots * n_q_heads * 2 * sizeof(float);
   cudaError_t e = cudaMalloc(&s->part_o, o_bytes);
@@ -974,6 +977,78 @@ extern "C" int pkv_decode_static(int device, const pkv_decode_args* a, void* out
   lo.lse_part = lse_out;
   return launch_decode(&s, a, lo, st);
 }
+
+// ------------------------------------------------------------------------- //
+// the small kernels of a decoder layer around the attention call
+// ------------------------------------------------------------------------- //
+extern "C" {
+
+int pkv_add_rmsnorm(int device, void* x, const void* delta, const void* weight, void* out, int32_t rows,
+                    int32_t hidden, float eps, int32_t dtype, void* stream) {
+  if (!x || !weight || !out) return fail(PKV_E_INVALID, "null pointer");
+  if (!is_16bit(dtype)) return fail(PKV_E_INVALID, "dtype must be PKV_F16 or PKV_BF16");
+  if (rows < 0 || hidden <= 0 || hidden % 8 || hidden > 12000)
+    return fail(PKV_E_INVALID, "rows %d hidden %d (a multiple of 8, at most 12000)", rows, hidden);
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(weight) |
+       reinterpret_cast<uintptr_t>(out)) & 15)
+    return fail(PKV_E_INVALID, "pointers must be 16-byte aligned");
+  if (rows == 0) return PKV_OK;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", device);
+  const size_t sm = (size_t)hidden * sizeof(float);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == PKV_BF16) pkv::add_rmsnorm_kernel<true><<<rows, 512, sm, st>>>(x, delta, weight, out, hidden, eps);
+  else                   pkv::add_rmsnorm_kernel<false><<<rows, 512, sm, st>>>(x, delta, weight, out, hidden, eps);
+  PKV_CUDA(cudaGetLastError());
+  return PKV_OK;
+}
+
+int pkv_rope_append(int device, const void* qkv, const int64_t* positions, const float* inv_freq, int32_t batch,
+                    int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim, void* q_out, void* k_pool,
+                    void* v_pool, int64_t page_stride, int64_t token_stride, int64_t head_stride,
+                    const int64_t* pages, const int64_t* slots, int32_t dtype, void* stream) {
+  if (!qkv || !positions || !inv_freq || !q_out) return fail(PKV_E_INVALID, "null pointer");
+  if (!is_16bit(dtype)) return fail(PKV_E_INVALID, "dtype must be PKV_F16 or PKV_BF16");
+  if (batch < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || head_dim % 2 || head_dim > 2048)
+    return fail(PKV_E_INVALID, "batch %d heads %d/%d head_dim %d", batch, n_q_heads, n_kv_heads, head_dim);
+  if ((k_pool || v_pool) && (!k_pool || !v_pool || !pages || !slots))
+    return fail(PKV_E_INVALID, "an append needs k_pool, v_pool, pages and slots");
+  if (batch == 0) return PKV_OK;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", device);
+  pkv::RopeParams p;
+  memset(&p, 0, sizeof p);
+  p.qkv = qkv; p.positions = positions; p.inv_freq = inv_freq; p.q_out = q_out;
+  p.k_pool = k_pool; p.v_pool = v_pool; p.pages = pages; p.slots = slots;
+  p.page_stride = page_stride; p.token_stride = token_stride; p.head_stride = head_stride;
+  p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim;
+  const dim3 grid(batch, n_q_heads + 2 * n_kv_heads);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == PKV_BF16) pkv::rope_append_kernel<true><<<grid, head_dim / 2, 0, st>>>(p);
+  else                   pkv::rope_append_kernel<false><<<grid, head_dim / 2, 0, st>>>(p);
+  PKV_CUDA(cudaGetLastError());
+  return PKV_OK;
+}
+
+int pkv_swiglu(int device, const void* gate_up, void* out, int32_t rows, int32_t ffn, int32_t dtype, void* stream) {
+  if (!gate_up || !out) return fail(PKV_E_INVALID, "null pointer");
+  if (!is_16bit(dtype)) return fail(PKV_E_INVALID, "dtype must be PKV_F16 or PKV_BF16");
+  if (rows < 0 || ffn <= 0 || ffn % 8) return fail(PKV_E_INVALID, "rows %d ffn %d (a multiple of 8)", rows, ffn);
+  if ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15)
+    return fail(PKV_E_INVALID, "pointers must be 16-byte aligned");
+  if (rows == 0) return PKV_OK;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", device);
+  const int64_t n8 = (int64_t)rows * (ffn / 8);
+  const unsigned int blocks = static_cast<unsigned int>((n8 + 255) / 256);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == PKV_BF16) pkv::swiglu_kernel<true><<<blocks, 256, 0, st>>>(gate_up, out, rows, ffn);
+  else                   pkv::swiglu_kernel<false><<<blocks, 256, 0, st>>>(gate_up, out, rows, ffn);
+  PKV_CUDA(cudaGetLastError());
+  return PKV_OK;
+}
+
+}  // extern "C"
 
 extern "C" int pkv_static_status(int device, void* stream, uint32_t* status_out) {
   if (device < 0 || device >= kStaticMaxDevices) return fail(PKV_E_INVALID, "device %d", device);

@@ -96,6 +96,7 @@ struct DecodeParams {
   unsigned int* seq_counter;   // [batch][n_kv_heads], zero between launches
   unsigned int* grp_counter;   // [(CTA groups + batch)][n_kv_heads], zero between launches
   int grp_slot0;               // first slot index of the per-group partials
+  int sib_slot0;               // first slot index of the second warps' parking slots (two warps per head)
   // adaptive split of the tile list: per-CTA (duration ns, tiles, weight) of the previous
   // launch on this shard; written for the next one.  Word 0 is the CTA count they refer to.
   const uint32_t* obs_read;
@@ -492,7 +493,8 @@ struct SmemLayout {
   static constexpr int kBarOff = kScaleOff + kScaleBytes;
   static constexpr int kNumBars = 2 * NSTAGE * kHeadsPerCta + 4 * NSTAGE;
   static constexpr int kAbortOff = kBarOff + kNumBars * 8;
-  static constexpr int kBoundOff = kAbortOff + 16;                     // tile range bounds per CTA
+  static constexpr int kSibOff = kAbortOff + 16;                       // [8] per-head hand-over counters (WPH = 2)
+  static constexpr int kBoundOff = kSibOff + 32;                       // tile range bounds per CTA
   static constexpr int kWeightOff = kBoundOff + (kMaxCtas + 1) * 4;    // split weights (floats)
   static constexpr int kPrefixOff = kWeightOff + kMaxCtas * 4;
   static constexpr int kTotal = kPrefixOff + (kMaxBatch + 1) * 4 + 1024;  // +1024: manual alignment
@@ -587,6 +589,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
         mbar_init(scale_full(ring, s), 1);
       }
     *abort_flag = 0;
+    for (int h = 0; h < kHeadsPerCta; ++h) reinterpret_cast<volatile int*>(sgen + L::kSibOff)[h] = 0;
     fence_barrier_init();
   }
   build_tile_prefix(prefix, p.seq_lens, p.batch, p.page_size, p.tiles_per_page, p.force_empty != 0);
@@ -822,44 +825,98 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
 
     // Q^T B-fragments: column n = g is q head kvh*G + g (zero beyond the group).
     // 16-bit pools: k-step ks covers d = 16ks..16ks+15 in the natural order.
-    // 1-byte pools: k index 2t+{0,1} of step ks is d = 16ks+4t+{0,1} and k index 2t+8+{0,1}
-    // is d = 16ks+4t+{2,3} (the order in which ldmatrix hands out code bytes).
-    uint32_t qf[8][2];
-    {
+    // 1-byte pools: the K codes go into 8-bit MMAs (m16n8k32) as they lie in shared memory,
+    // so q has to become 8-bit terms: k-step kp covers d = 32kp..32kp+31, register 0 of a
+    // term holds d = 32kp+4t..+3 and register 1 d = 32kp+16+4t..+3, one byte each.
+    //   int8 codes: q is scaled to 16-bit integers per head (absmax -> 32767) and split into
+    //     a signed high byte and an unsigned low byte: two integer MMAs per k-step,
+    //     score = (256 acc_hi + acc_lo) * absmax / 32767, exact in int32.
+    //   e4m3 codes: q is scaled by a power of two per head (absmax into [128, 256)) and split
+    //     into two e4m3 terms q = t1 + t2, t2 the rounding of what t1 left: eight significant
+    //     bits, which holds a bf16 value exactly (down to 2^-17 of the head's absmax) and
+    //     rounds an fp16 one to that precision.  A product of two e4m3 values is exact in the
+    //     fp32 accumulator.
+    constexpr int kQTerms = 2;
+    uint32_t qf[kQuant ? kQTerms * 4 : 8][2];
+    float qmul0 = 1.f, qmul1 = 1.f;      // what the 8-bit terms of score columns 2t, 2t+1 must be multiplied by
+    if constexpr (!kQuant) {
       const uint32_t* qrow = reinterpret_cast<const uint32_t*>(
           reinterpret_cast<const uint16_t*>(p.q) +
           ((int64_t)s * p.n_q_heads + (int64_t)kvh * G + g) * kHeadDim);
       const bool have = active && g < G;
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        if constexpr (kQuant) {
-          qf[ks][0] = have ? __ldcg(qrow + ks * 8 + 2 * t) : 0u;
-          qf[ks][1] = have ? __ldcg(qrow + ks * 8 + 2 * t + 1) : 0u;
-          if constexpr (QBF16) {
-            qf[ks][0] = bf16x2_to_half2(qf[ks][0]);
-            qf[ks][1] = bf16x2_to_half2(qf[ks][1]);
-          }
+        qf[ks][0] = have ? __ldcg(qrow + ks * 8 + t) : 0u;
+        qf[ks][1] = have ? __ldcg(qrow + ks * 8 + 4 + t) : 0u;
+      }
+    } else {
+      const uint16_t* qrow = reinterpret_cast<const uint16_t*>(p.q) +
+                             ((int64_t)s * p.n_q_heads + (int64_t)kvh * G + g) * kHeadDim;
+      const bool have = active && g < G;
+      auto widen = [](const uint2& raw, float (&v)[4]) {
+        if constexpr (QBF16) {
+          const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+          const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+          v[0] = __low2float(x); v[1] = __high2float(x); v[2] = __low2float(y); v[3] = __high2float(y);
         } else {
-          qf[ks][0] = have ? __ldcg(qrow + ks * 8 + t) : 0u;
-          qf[ks][1] = have ? __ldcg(qrow + ks * 8 + 4 + t) : 0u;
+          const __half2 x = *reinterpret_cast<const __half2*>(&raw.x);
+          const __half2 y = *reinterpret_cast<const __half2*>(&raw.y);
+          v[0] = __low2float(x); v[1] = __high2float(x); v[2] = __low2float(y); v[3] = __high2float(y);
+        }
+      };
+      uint2 qraw[8];
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int d0 = 32 * (i >> 1) + 16 * (i & 1) + 4 * t;
+        qraw[i] = have ? __ldcg(reinterpret_cast<const uint2*>(qrow + d0)) : make_uint2(0u, 0u);
+        float v[4];
+        widen(qraw[i], v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) amax = fmaxf(amax, fabsf(v[e]));
+      }
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));      // the head's 128 dims
+      const bool live = amax > 1e-30f && amax < 3e38f;
+      float pre, post;
+      if constexpr (KVT == kKvInt8) {
+        pre = live ? 32767.f / amax : 0.f;
+        post = live ? amax * (1.f / 32767.f) : 0.f;
+      } else {
+        const int e2 = (int)((__float_as_uint(amax) >> 23) & 255u) - 127;      // amax in [2^e2, 2^(e2+1))
+        pre = live ? __uint_as_float((uint32_t)(127 + 7 - e2) << 23) : 0.f;
+        post = live ? __uint_as_float((uint32_t)(127 - 7 + e2) << 23) : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int kp = i >> 1, half = i & 1;
+        float qv[4];
+        widen(qraw[i], qv);
+        if constexpr (KVT == kKvInt8) {
+          uint32_t hi = 0u, lo = 0u;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int qi = __float2int_rn(qv[e] * pre);             // |qi| <= 32767
+            hi |= ((uint32_t)(qi >> 8) & 255u) << (8 * e);
+            lo |= ((uint32_t)qi & 255u) << (8 * e);
+          }
+          qf[kp][half] = hi;
+          qf[4 + kp][half] = lo;
+        } else {
+          float r[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) r[e] = qv[e] * pre;
+#pragma unroll
+          for (int term = 0; term < kQTerms; ++term) {
+            const uint32_t p01 = pack_e4m3x2(r[0], r[1]), p23 = pack_e4m3x2(r[2], r[3]);
+            qf[term * 4 + kp][half] = p01 | (p23 << 16);
+            const float2 f01 = unpack_e4m3x2(p01), f23 = unpack_e4m3x2(p23);
+            r[0] -= f01.x; r[1] -= f01.y; r[2] -= f23.x; r[3] -= f23.y;
+          }
         }
       }
-    }
-    // int8 pools: K codes enter the MMA as (code + 1152); 1152 * sum_d q[head][d] comes
-    // off each score.  The sums are taken over the fp16 values the MMA really uses.
-    float qb0 = 0.f, qb1 = 0.f;          // for score columns (q heads) 2t and 2t+1
-    if constexpr (KVT == kKvInt8) {
-      float qs = 0.f;
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const __half2 x = *reinterpret_cast<const __half2*>(&qf[ks][0]);
-        const __half2 y = *reinterpret_cast<const __half2*>(&qf[ks][1]);
-        qs += (__low2float(x) + __high2float(x)) + (__low2float(y) + __high2float(y));
-      }
-      qs += __shfl_xor_sync(0xffffffffu, qs, 1);
-      qs += __shfl_xor_sync(0xffffffffu, qs, 2);      // all of head g's 128 dims
-      qb0 = 1152.f * __shfl_sync(0xffffffffu, qs, (2 * t) * 4);
-      qb1 = 1152.f * __shfl_sync(0xffffffffu, qs, (2 * t + 1) * 4);
+      qmul0 = __shfl_sync(0xffffffffu, post, (2 * t) * 4) * p.scale_log2;
+      qmul1 = __shfl_sync(0xffffffffu, post, (2 * t + 1) * 4) * p.scale_log2;
     }
     float o[8][4];
 #pragma unroll
@@ -890,29 +947,40 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       if (active) {
         float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
         if constexpr (kQuant) {
-          // [16 tok][128 B] codes: one ldmatrix.x4 = two 16-byte chunks = two k-steps.
+          // [16 tok][128 B] codes: one ldmatrix.x4 = two 16-byte chunks = the A fragment of
+          // one k-step of 32 dims (r0: tok g, bytes 4t..; r1: tok g+8; r2, r3: the next chunk).
+          if constexpr (KVT == kKvInt8) {
+            int ih[4] = {0, 0, 0, 0}, il[4] = {0, 0, 0, 0};
 #pragma unroll
-          for (int kp = 0; kp < 4; ++kp) {
-            uint32_t r[4], a[4];
-            const uint32_t chunk = (kp << 1) | kcsel;
-            ldmatrix_x4(r, sk + krow_off + ((chunk ^ kx) << 4));
-            // r0: tok g, chunk 2kp; r1: tok g+8, chunk 2kp; r2, r3: chunk 2kp+1
-            constexpr bool F8 = KVT == kKvFp8;
-            codes_to_half2<F8, false>(r[0], kQuantSelK0<F8>(), kQuantSelK1<F8>(), a[0], a[2]);
-            codes_to_half2<F8, false>(r[1], kQuantSelK0<F8>(), kQuantSelK1<F8>(), a[1], a[3]);
-            mma_16816<false>(sa, a, qf[2 * kp][0], qf[2 * kp][1]);
-            codes_to_half2<F8, false>(r[2], kQuantSelK0<F8>(), kQuantSelK1<F8>(), a[0], a[2]);
-            codes_to_half2<F8, false>(r[3], kQuantSelK0<F8>(), kQuantSelK1<F8>(), a[1], a[3]);
-            mma_16816<false>(sb, a, qf[2 * kp + 1][0], qf[2 * kp + 1][1]);
+            for (int kp = 0; kp < 4; ++kp) {
+              uint32_t r[4];
+              const uint32_t chunk = (kp << 1) | kcsel;
+              ldmatrix_x4(r, sk + krow_off + ((chunk ^ kx) << 4));
+              mma_16832_s8<false>(ih, r, qf[kp][0], qf[kp][1]);
+              mma_16832_s8<true>(il, r, qf[4 + kp][0], qf[4 + kp][1]);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sa[i] = (float)(ih[i] * 256 + il[i]);
+          } else {
+#pragma unroll
+            for (int kp = 0; kp < 4; ++kp) {
+              uint32_t r[4];
+              const uint32_t chunk = (kp << 1) | kcsel;
+              ldmatrix_x4(r, sk + krow_off + ((chunk ^ kx) << 4));
+              mma_16832_e4m3(sa, r, qf[kp][0], qf[kp][1]);
+              mma_16832_e4m3(sb, r, qf[4 + kp][0], qf[4 + kp][1]);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sa[i] += sb[i];
           }
           // per-token K scales (rows g and g+8 of the score tile)
           got = pipe_wait(scale_full(0, stage), ph, abort_flag, pipe_deadline);
           if (!got) { if (lane == 0) pipe_failed(p, abort_flag); return; }
           const __half* ksc = reinterpret_cast<const __half*>(sgen + L::kScaleOff + stage * L::kScaleSlot);
-          const float k0 = __half2float(ksc[g * scale_stride + hh]) * p.scale_log2;
-          const float k1 = __half2float(ksc[(g + 8) * scale_stride + hh]) * p.scale_log2;
-          sc[0] = (sa[0] + sb[0] - qb0) * k0; sc[1] = (sa[1] + sb[1] - qb1) * k0;
-          sc[2] = (sa[2] + sb[2] - qb0) * k1; sc[3] = (sa[3] + sb[3] - qb1) * k1;
+          const float k0 = __half2float(ksc[g * scale_stride + hh]);
+          const float k1 = __half2float(ksc[(g + 8) * scale_stride + hh]);
+          sc[0] = sa[0] * (k0 * qmul0); sc[1] = sa[1] * (k0 * qmul1);
+          sc[2] = sa[2] * (k1 * qmul0); sc[3] = sa[3] * (k1 * qmul1);
         } else {
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
@@ -980,6 +1048,8 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
           mk01 = (2 * t < valid ? 0x0000ffffu : 0u) | (2 * t + 1 < valid ? 0xffff0000u : 0u);
           mk23 = (2 * t + 8 < valid ? 0x0000ffffu : 0u) | (2 * t + 9 < valid ? 0xffff0000u : 0u);
         }
+        [[maybe_unused]] const uint32_t bias_a[4] = {0x64806480u, 0x64806480u, 0x64806480u, 0x64806480u};
+        [[maybe_unused]] const uint32_t nb0 = b0 ^ 0x80008000u, nb1 = b1 ^ 0x80008000u;      // -P
         if constexpr (kQuant) {
           // Transposed 8x8 "b16" loads over code bytes deliver, per thread, the byte pairs
           // (d = 2g, 2g+1) of tokens 2t and 2t+1: bytes (0,2) are row d = 16c+2g of V^T and
@@ -991,14 +1061,22 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
             const uint32_t chunk = (jp << 1) | kcsel;
             ldmatrix_x4_trans(r, sv + krow_off + ((chunk ^ kx) << 4));
             // r0: toks 0-7, chunk 2jp; r1: toks 8-15, chunk 2jp; r2, r3: chunk 2jp+1
-            codes_to_half2<KVT == kKvFp8>(r[0], kQuantSelV0<KVT == kKvFp8>(), kQuantSelV1<KVT == kKvFp8>(), a[0], a[1]);
-            codes_to_half2<KVT == kKvFp8>(r[1], kQuantSelV0<KVT == kKvFp8>(), kQuantSelV1<KVT == kKvFp8>(), a[2], a[3]);
+            // int8 codes enter as (code + 1152), three instructions per register instead of
+            // five; a second MMA with the constant 1152 and -P takes the bias off again.  Its
+            // rounding error is 2^-24 * 1152 * sum(P) per tile at most, i.e. below 1e-4 code
+            // units of the normalised output.  Rows past `valid` are zero in the first MMA
+            // and carry P = 0 in the second.
+            constexpr bool F8 = KVT == kKvFp8;
+            codes_to_half2<F8, F8>(r[0], kQuantSelV0<F8>(), kQuantSelV1<F8>(), a[0], a[1]);
+            codes_to_half2<F8, F8>(r[1], kQuantSelV0<F8>(), kQuantSelV1<F8>(), a[2], a[3]);
             if (valid < kTileTok) { a[0] &= mk01; a[1] &= mk01; a[2] &= mk23; a[3] &= mk23; }
             mma_16816<false>(o[2 * jp], a, b0, b1);
-            codes_to_half2<KVT == kKvFp8>(r[2], kQuantSelV0<KVT == kKvFp8>(), kQuantSelV1<KVT == kKvFp8>(), a[0], a[1]);
-            codes_to_half2<KVT == kKvFp8>(r[3], kQuantSelV0<KVT == kKvFp8>(), kQuantSelV1<KVT == kKvFp8>(), a[2], a[3]);
+            if constexpr (!F8) mma_16816<false>(o[2 * jp], bias_a, nb0, nb1);
+            codes_to_half2<F8, F8>(r[2], kQuantSelV0<F8>(), kQuantSelV1<F8>(), a[0], a[1]);
+            codes_to_half2<F8, F8>(r[3], kQuantSelV0<F8>(), kQuantSelV1<F8>(), a[2], a[3]);
             if (valid < kTileTok) { a[0] &= mk01; a[1] &= mk01; a[2] &= mk23; a[3] &= mk23; }
             mma_16816<false>(o[2 * jp + 1], a, b0, b1);
+            if constexpr (!F8) mma_16816<false>(o[2 * jp + 1], bias_a, nb0, nb1);
           }
         } else {
 #pragma unroll
@@ -1030,9 +1108,54 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
         l0 += __shfl_xor_sync(0xffffffffu, l0, off);
         l1 += __shfl_xor_sync(0xffffffffu, l1, off);
       }
-      const int slot = (blockIdx.x + s) * WPH + par;
-      const int64_t hbase = (int64_t)slot * p.n_q_heads + (int64_t)kvh * G;
       const int h0 = 2 * t, h1 = 2 * t + 1;
+      // Two warps per head (1-byte pools): the second warp parks its partial in a slot of
+      // its own and hands over; the first folds it into its registers, so the CTA leaves
+      // ONE slot per (sequence, kv-head) as with one warp per head.  Both warps walk the
+      // same segments in the same order, so the hand-over counter is the sequence number + 1.
+      const int slot = (WPH > 1 && par == 1) ? p.sib_slot0 + blockIdx.x + s : blockIdx.x + s;
+      const int64_t hbase = (int64_t)slot * p.n_q_heads + (int64_t)kvh * G;
+      if constexpr (WPH > 1) {
+        volatile int* sib = reinterpret_cast<volatile int*>(sgen + L::kSibOff) + hh;
+        if (par == 0) {
+          int ok = 1;
+          if (lane == 0) {
+            ok = 0;
+            for (uint32_t w = 0;; ++w) {
+              if (*sib > s) { ok = 1; break; }
+              if (*abort_flag) break;
+              if ((w & 63u) == 63u && global_ns() > pipe_deadline) { pipe_failed(p, abort_flag); break; }
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) return;
+          __syncwarp();
+          const int64_t sbase = (int64_t)(p.sib_slot0 + blockIdx.x + s) * p.n_q_heads + (int64_t)kvh * G;
+          const float2 sm0 = h0 < G ? __ldcg(reinterpret_cast<const float2*>(p.part_ml) + sbase + h0) : make_float2(-INFINITY, 0.f);
+          const float2 sm1 = h1 < G ? __ldcg(reinterpret_cast<const float2*>(p.part_ml) + sbase + h1) : make_float2(-INFINITY, 0.f);
+          const float mn0 = fmaxf(m0, sm0.x), mn1 = fmaxf(m1, sm1.x);
+          // factors of own and sibling rows; a side without tokens (m = -inf) counts as zero
+          const float a0 = m0 == -INFINITY ? 0.f : fast_exp2(m0 - mn0), b0s = sm0.x == -INFINITY ? 0.f : fast_exp2(sm0.x - mn0);
+          const float a1 = m1 == -INFINITY ? 0.f : fast_exp2(m1 - mn1), b1s = sm1.x == -INFINITY ? 0.f : fast_exp2(sm1.x - mn1);
+          l0 = l0 * a0 + sm0.y * b0s; l1 = l1 * a1 + sm1.y * b1s;
+          m0 = mn0; m1 = mn1;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int d = 16 * j + 2 * g;          // 1-byte pools: rows g, g+8 of m-tile j are d, d+1
+            float s00 = 0.f, s02 = 0.f, s01 = 0.f, s03 = 0.f;
+            if (h0 < G) {
+              const float2 v = __ldcg(reinterpret_cast<const float2*>(p.part_o + (sbase + h0) * kHeadDim + d));
+              s00 = v.x; s02 = v.y;
+            }
+            if (h1 < G) {
+              const float2 v = __ldcg(reinterpret_cast<const float2*>(p.part_o + (sbase + h1) * kHeadDim + d));
+              s01 = v.x; s03 = v.y;
+            }
+            o[j][0] = o[j][0] * a0 + s00 * b0s; o[j][2] = o[j][2] * a0 + s02 * b0s;
+            o[j][1] = o[j][1] * a1 + s01 * b1s; o[j][3] = o[j][3] * a1 + s03 * b1s;
+          }
+        }
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         // accumulator rows g and g+8 of m-tile j: d = 16j+g, 16j+g+8 (16-bit pools) or
@@ -1052,6 +1175,14 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
         if (h0 < G) { p.part_ml[(hbase + h0) * 2] = m0; p.part_ml[(hbase + h0) * 2 + 1] = l0; }
         if (h1 < G) { p.part_ml[(hbase + h1) * 2] = m1; p.part_ml[(hbase + h1) * 2 + 1] = l1; }
       }
+      if constexpr (WPH > 1) {
+        if (par == 1) {
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) reinterpret_cast<volatile int*>(sgen + L::kSibOff)[hh] = s + 1;
+          continue;                  // the first warp of the pair takes it from here
+        }
+      }
     }
 
     if (p.fuse) {
@@ -1060,7 +1191,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       // CTA-wide meeting, so the other warps run straight into the next sequence.
       const int t0s = prefix[s], t1s = prefix[s + 1];
       const int c0 = find_cta(bound, p.n_cta_x, t0s), c1 = find_cta(bound, p.n_cta_x, t1s - 1);
-      const int slot_lo = (c0 + s) * WPH, slot_hi = (c1 + s) * WPH + WPH - 1;
+      const int slot_lo = c0 + s, slot_hi = c1 + s;
       __threadfence();
       __syncwarp();
       int last = 0;
@@ -1085,14 +1216,13 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
         if (lane == 0) {
           unsigned int* ctr = p.grp_counter + (size_t)(gi + s) * p.n_kv_heads + kvh;
           const unsigned int prev = atomicAdd(ctr, 1u);
-          glast = prev == (unsigned int)((cg1 - cg0 + 1) * WPH - 1);
+          glast = prev == (unsigned int)(cg1 - cg0);
           if (glast) *ctr = 0;
           __threadfence();
         }
         glast = __shfl_sync(0xffffffffu, glast, 0);
         if (glast) {
-          combine_group<(WPH > 1)>(p, s, kvh * G, G, (cg0 + s) * WPH, (cg1 + s) * WPH + WPH - 1, lane,
-                                   p.grp_slot0 + gi + s);
+          combine_group<(WPH > 1)>(p, s, kvh * G, G, cg0 + s, cg1 + s, lane, p.grp_slot0 + gi + s);
           __threadfence();
           __syncwarp();
           if (lane == 0) {

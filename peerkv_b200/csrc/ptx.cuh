@@ -107,6 +107,46 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
   }
 }
 
+// D(16x8, s32) += A(16x32 s8, row) * B(32x8, col); B signed (BU8 = false) or unsigned bytes.
+template <bool BU8>
+__device__ __forceinline__ void mma_16832_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (BU8) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0, %1, %2, %3}, "
+        "{%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, "
+        "{%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+// D(16x8, f32) += A(16x32 e4m3, row) * B(32x8 e4m3, col): products of two e4m3 values are
+// exact in the fp32 accumulator.
+__device__ __forceinline__ void mma_16832_e4m3(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0, %1, %2, %3}, "
+      "{%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// two floats -> two e4m3 bytes (hi from `hi`, lo from `lo`), round to nearest, saturating
+__device__ __forceinline__ uint32_t pack_e4m3x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// two e4m3 bytes (low 16 bits of v) -> two floats
+__device__ __forceinline__ float2 unpack_e4m3x2(uint32_t v) {
+  uint32_t h;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h) : "h"(static_cast<unsigned short>(v)));
+  const __half2 hh = *reinterpret_cast<const __half2*>(&h);
+  return make_float2(__low2float(hh), __high2float(hh));
+}
+
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   if constexpr (BF16) {

@@ -63,6 +63,19 @@ class DistPeerGroup:
     def status(self) -> int:
         return self.shard.status() | self.xchg.status()
 
+    def barrier(self):
+        dist.barrier(group=self.pg)
+
+    # -- a sequence of steps as one CUDA graph per rank (every rank does the same) ------- #
+    def capture_begin(self):
+        self.xchg.capture_begin()
+
+    def capture_end(self) -> int:
+        return self.xchg.capture_end(ops._stream(self.device))
+
+    def replayed(self):
+        self.xchg.replayed()
+
     def resync(self):
         """After an error on any rank: all ranks agree on the largest epoch reached, so the
         next step's tags mean the same thing everywhere (a collective; call it on every rank)."""

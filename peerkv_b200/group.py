@@ -60,6 +60,21 @@ class Exchange:
         check(_lib.lib().pkv_exchange_epoch(self._h, C.byref(v)))
         return int(v.value)
 
+    def capture_begin(self):
+        """Before the stream capture of a sequence of steps starts."""
+        check(_lib.lib().pkv_exchange_capture_begin(self._h))
+
+    def capture_end(self, stream: int) -> int:
+        """Inside the capture, after its last step: adds the node that advances the
+        device-resident epoch base.  Returns the number of steps the graph holds."""
+        n = C.c_uint64()
+        check(_lib.lib().pkv_exchange_capture_end(self._h, stream, C.byref(n)))
+        return int(n.value)
+
+    def replayed(self):
+        """After every launch of the captured graph: the host's epoch follows."""
+        check(_lib.lib().pkv_exchange_replayed(self._h))
+
     def resync(self, epoch: int):
         """Sets the epoch (every rank passes the same value) after a failed or skipped step."""
         check(_lib.lib().pkv_exchange_resync(self._h, int(epoch)))

@@ -6,14 +6,14 @@ Mirrors, for this path only, PeerKV's host-side cost helpers and selector:
   partial_bytes, balanced_partition            umallm/multigpu.py:351-359, 362-377
   PeerKVCostModel.decode_step_parallel_us      umallm/multigpu.py:191-215
   PeerKVCostModel.max_context_for_slo_parallel umallm/multigpu.py:217-239
-  OperatingPoint, PeerState, select_point,
-  enforce_do_no_harm (the CFK-relevant rules)  umallm/elastic_policy.py:56-62, 261-284, 318-365
+(the operating-point selector and the do-no-harm rules are in elastic_policy.py)
 
 The reference's constants are dual-A100 measurements (773 / 273 GB/s, 12-24 us set-up).
 The defaults here are what this library measures on B200 (effective KV read bandwidth
 of the decode kernel, cost of one exchange); `PeerKVCostModel.calibrate` refits them
-from two timed single-GPU points and one N-GPU point, the recipe of
-umallm/runtime/calibration.py:76-148.
+from two timed single-GPU points and one N-GPU point, and calibration.calibrate_box
+measures those points with the library's own kernels (the recipe of
+umallm/runtime/calibration.py:76-148).
 
 The page -> GPU maps themselves are made on the device (`pkv_split_block_table`,
 group.PeerGroup.split_table); `PagePlacer` is the allocation-time counterpart that
@@ -21,9 +21,8 @@ decides where a NEW page goes.
 """
 from __future__ import annotations
 
-import enum
 import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
 # measured with this library on B200 (bf16, Hkv 8, D 128, 16-token pages)
@@ -106,98 +105,6 @@ class PeerKVCostModel:
         tb, tt = multi_pt
         m.exchange_us = max(0.0, tt - m.kernel_fixed_us - (tb / n_devices) * slope)
         return m
-
-
-class OperatingPoint(enum.Enum):
-    SINGLE = "single"                   # the whole context on the query's GPU
-    CFK = "compute_follows_kv"          # KV sharded over peers, partials exchanged
-    INFEASIBLE = "infeasible"
-
-
-@dataclass
-class PeerState:
-    """Live state of the peer GPUs at admission time (umallm/elastic_policy.py:77-82)."""
-    n_peers: int = 7
-    hbm_free_bytes: int = B200_HBM_BYTES          # per peer, available to KV
-    compute_idle: bool = True                     # may the peers lend attention compute?
-    nvlink_bw_gbps: float = B200_NVLINK_GBPS      # 0 => link down / degraded
-
-
-@dataclass
-class Decision:
-    point: OperatingPoint
-    predicted_us: float
-    admissible: set = field(default_factory=set)
-    meets_deadline: bool = True
-    reason: str = ""
-
-
-class DoNoHarmViolation(RuntimeError):
-    """A chosen operating point would break a do-no-harm rule."""
-
-
-def admissible_points(kv_bytes: int, local_free_bytes: int, peer: PeerState) -> set:
-    pts = set()
-    if kv_bytes <= local_free_bytes:
-        pts.add(OperatingPoint.SINGLE)
-    n = peer.n_peers + 1
-    share = math.ceil(kv_bytes / n)
-    if peer.n_peers > 0 and peer.compute_idle and peer.nvlink_bw_gbps > 0 \
-            and share <= peer.hbm_free_bytes and share <= local_free_bytes:
-        pts.add(OperatingPoint.CFK)
-    return pts
-
-
-def select_point(kv_bytes: int, local_free_bytes: int, peer: PeerState,
-                 model: Optional[PeerKVCostModel] = None, deadline_us: Optional[float] = None,
-                 block_bytes: int = 65536) -> Decision:
-    """Pick the admissible point with the lowest predicted attention time per layer;
-    flag an SLO miss instead of refusing (umallm/elastic_policy.py:261-284)."""
-    model = model or PeerKVCostModel()
-    adm = admissible_points(kv_bytes, local_free_bytes, peer)
-    if not adm:
-        return Decision(OperatingPoint.INFEASIBLE, math.inf, adm, False, "no admissible point")
-    blocks = math.ceil(kv_bytes / block_bytes)
-    preds = {}
-    if OperatingPoint.SINGLE in adm:
-        preds[OperatingPoint.SINGLE] = model.decode_step_parallel_us([blocks], block_bytes)
-    if OperatingPoint.CFK in adm:
-        split = balanced_partition(blocks, [model.hbm_gbps] * (peer.n_peers + 1))
-        preds[OperatingPoint.CFK] = model.decode_step_parallel_us(split, block_bytes, heads=32, head_dim=128)
-    best = min(preds, key=preds.get)
-    why = []
-    if OperatingPoint.SINGLE not in adm:
-        why.append("context does not fit one GPU")
-    if OperatingPoint.CFK not in adm:
-        why.append("peers busy, full or unreachable -> single GPU only")
-    meets = deadline_us is None or preds[best] <= deadline_us
-    return Decision(best, preds[best], adm, meets, "; ".join(why) or "fastest admissible")
-
-
-def enforce_do_no_harm(point: OperatingPoint, kv_bytes: int, local_free_bytes: int,
-                       peer: PeerState, model: Optional[PeerKVCostModel] = None,
-                       block_bytes: int = 65536) -> OperatingPoint:
-    """Rules of umallm/elastic_policy.py:318-365 that concern this path:
-    R1-busy (peers computing -> CFK forbidden), R1-route (link down -> CFK forbidden),
-    R1-fit, restated for a path that can be FASTER than one GPU: a context that fits one
-    GPU may still be sharded, but only when the model predicts it is not slower."""
-    model = model or PeerKVCostModel()
-    if point is OperatingPoint.CFK:
-        if not peer.compute_idle:
-            raise DoNoHarmViolation("R1-busy: peer compute-busy, CFK forbidden")
-        if peer.nvlink_bw_gbps <= 0 or peer.n_peers <= 0:
-            raise DoNoHarmViolation("R1-route: no usable NVLink path to a peer, CFK forbidden")
-        if kv_bytes <= local_free_bytes:
-            blocks = math.ceil(kv_bytes / block_bytes)
-            single = model.decode_step_parallel_us([blocks], block_bytes)
-            split = balanced_partition(blocks, [model.hbm_gbps] * (peer.n_peers + 1))
-            cfk = model.decode_step_parallel_us(split, block_bytes, heads=32, head_dim=128)
-            if cfk > single:
-                raise DoNoHarmViolation(
-                    f"R1-fit: fits one GPU and sharding is predicted slower ({cfk:.1f} > {single:.1f} us)")
-    if point is OperatingPoint.SINGLE and kv_bytes > local_free_bytes:
-        raise DoNoHarmViolation("SINGLE chosen but the context does not fit one GPU")
-    return point
 
 
 def capacity_spill_split(pages_per_seq: Sequence[int], seq_lens: Sequence[int], page_size: int,

@@ -355,72 +355,3 @@ def test_quantised_kv_decode(dev, fmt, qdtype, Hq, Hkv):
     rf, _ = orc.paged_partial_oracle(q, pool, bt, sl)
     tol = 4e-2 if fmt == "int8" else 0.3           # a 1-token sequence returns V itself: up to 2^-4 relative in e4m3
     assert (out.float().cpu() - rf)[has].abs().max() < tol
-
-
-def test_decoder_step_matches_torch_attention(dev):
-    """The Llama-style decode step (peerkv_b200/decoder.py) with its attention on the
-    library vs the same step with attention computed by the oracle on the gathered KV:
-    small geometry (2 layers, 8/2 heads of 128), paged KV with one appended token."""
-    import ctypes as C
-    import math
-    from peerkv_b200 import _lib, ops
-    from peerkv_b200.decoder import DecodeStep, LlamaGeometry, ModelWeights, ShardedKVLayer, make_args
-    torch.manual_seed(0)
-    g = LlamaGeometry(n_layers=2, hidden=1024, n_q_heads=8, n_kv_heads=2, head_dim=128, ffn=2048, vocab=512)
-    B, bs = 3, 16
-    lens = [48, 160, 16]                                   # whole pages; the new token opens a new page
-    n_pages = [L // bs for L in lens]
-    total = sum(n_pages)
-    W = max(n_pages) + 1
-    layers, refs = [], []
-    for li in range(g.n_layers):
-        pool = torch.zeros(2, total + B, bs, g.n_kv_heads, g.head_dim, dtype=torch.bfloat16, device=dev)
-        pool[:, :total].normal_()
-        tab = torch.zeros(B, W, dtype=torch.int32, device=dev)
-        k = 0
-        for i, n in enumerate(n_pages):
-            tab[i, :n] = torch.arange(k, k + n, dtype=torch.int32)
-            tab[i, n] = total + i
-            k += n
-        ln = torch.tensor([L + 1 for L in lens], dtype=torch.int32, device=dev)
-        layers.append(ShardedKVLayer(pool, tab, ln))
-    w = ModelWeights(g, dev)
-    shard = ops.Shard(dev, B, g.n_q_heads)
-    qbuf = torch.zeros(B, g.n_q_heads, g.head_dim, dtype=torch.bfloat16, device=dev)
-    largs = [make_args(qbuf, l, 1.0 / math.sqrt(g.head_dim)) for l in layers]
-    L_ = _lib.lib()
-
-    def attend_lib(li, q, out):
-        qbuf.copy_(q)
-        _lib.check(L_.pkv_decode(shard._h, C.byref(largs[li]), out.data_ptr(), _lib.PKV_BF16, None, ops._stream(dev)))
-
-    captured = []
-
-    def attend_ref(li, q, out):
-        l = layers[li]
-        o, _ = orc.paged_partial_oracle(q.cpu(), l.pool.cpu(), l.table.cpu(), l.lens.cpu())
-        out.copy_(o.to(out.dtype).to(dev))
-        captured.append(o)
-
-    append = (torch.arange(total, total + B, device=dev), torch.zeros(B, dtype=torch.int64, device=dev))
-    tokens = torch.tensor([5, 17, 400], device=dev)
-    pos = torch.tensor(lens, device=dev)
-    pools0 = [l.pool.clone() for l in layers]
-    nxt_lib = DecodeStep(g, w, layers, attend_lib, append).home_step(tokens, pos)
-    k_written = layers[0].pool[0, total:total + B, 0].clone()
-    for l, p0 in zip(layers, pools0):
-        l.pool.copy_(p0)
-    nxt_ref = DecodeStep(g, w, layers, attend_ref, append).home_step(tokens, pos)
-    assert shard.status() == 0
-    assert torch.equal(layers[0].pool[0, total:total + B, 0], k_written)      # the append itself
-    assert k_written.abs().sum() > 0
-    assert torch.equal(nxt_lib, nxt_ref)
-    # the same step with the non-attention pieces replayed as CUDA graphs
-    for l, p0 in zip(layers, pools0):
-        l.pool.copy_(p0)
-    ds = DecodeStep(g, w, layers, attend_lib, append)
-    ds.capture(B)
-    for l, p0 in zip(layers, pools0):
-        l.pool.copy_(p0)
-    assert torch.equal(ds.home_step(tokens, pos), nxt_ref)
-    assert torch.equal(layers[0].pool[0, total:total + B, 0], k_written)

@@ -58,32 +58,25 @@ def test_calibrate_recovers_constants():
         pl.PeerKVCostModel.calibrate({1 << 30: 50.0, 2 << 30: 40.0}, multi, 8)   # time falls with size
 
 
-def test_selector_and_do_no_harm():
-    peer = pl.PeerState(n_peers=7)
-    big = 400 * 1024 ** 3                         # does not fit one GPU
-    d = pl.select_point(big, pl.B200_HBM_BYTES, peer)
-    assert d.point is pl.OperatingPoint.CFK and "does not fit" in d.reason
-    tiny = 16 * 1024 ** 2                         # sharding 16 MiB is slower than reading it
-    d = pl.select_point(tiny, pl.B200_HBM_BYTES, peer)
-    assert d.point is pl.OperatingPoint.SINGLE
-    mid = 8 * 1024 ** 3                           # 8 GiB: sharding wins
-    assert pl.select_point(mid, pl.B200_HBM_BYTES, peer).point is pl.OperatingPoint.CFK
-    busy = pl.PeerState(n_peers=7, compute_idle=False)
-    assert pl.select_point(mid, pl.B200_HBM_BYTES, busy).point is pl.OperatingPoint.SINGLE
-    assert pl.select_point(big, pl.B200_HBM_BYTES, busy).point is pl.OperatingPoint.INFEASIBLE
-    with pytest.raises(pl.DoNoHarmViolation, match="R1-busy"):
-        pl.enforce_do_no_harm(pl.OperatingPoint.CFK, mid, pl.B200_HBM_BYTES, busy)
-    with pytest.raises(pl.DoNoHarmViolation, match="R1-route"):
-        pl.enforce_do_no_harm(pl.OperatingPoint.CFK, mid, pl.B200_HBM_BYTES,
-                              pl.PeerState(n_peers=7, nvlink_bw_gbps=0.0))
-    with pytest.raises(pl.DoNoHarmViolation, match="R1-fit"):
-        pl.enforce_do_no_harm(pl.OperatingPoint.CFK, tiny, pl.B200_HBM_BYTES, peer)
-    with pytest.raises(pl.DoNoHarmViolation):
-        pl.enforce_do_no_harm(pl.OperatingPoint.SINGLE, big, pl.B200_HBM_BYTES, peer)
-    assert pl.enforce_do_no_harm(pl.OperatingPoint.CFK, mid, pl.B200_HBM_BYTES, peer) is pl.OperatingPoint.CFK
-    # deadline flagging, not refusal
-    d = pl.select_point(big, pl.B200_HBM_BYTES, peer, deadline_us=1.0)
-    assert d.point is pl.OperatingPoint.CFK and not d.meets_deadline
+def test_capacity_spill_split_matches_the_oracle():
+    import numpy as np
+    from oracle import peerkv_oracle as orc
+    rng = np.random.default_rng(0)
+    for _ in range(25):
+        B, N, bs = int(rng.integers(1, 9)), int(rng.integers(1, 6)), 16
+        lens = rng.integers(1, 3000, size=B)
+        pages = (lens + bs - 1) // bs
+        caps = rng.uniform(0.5, 1.0, size=N)
+        start = np.concatenate([[0], np.cumsum(pages)[:-1]])
+        bt = [list(range(int(s0), int(s0 + p))) for s0, p in zip(start, pages)]
+        tab, tok, used = pl.capacity_spill_split(pages, lens, bs, caps)
+        ref = orc.capacity_spill_shards(bt, lens, bs, list(caps))
+        assert int(used.sum()) == int(pages.sum())
+        for g, (t, l) in enumerate(ref):
+            assert (l.numpy() == tok[g]).all()
+            flat = [int(x) for i in range(B) for x in t[i, :-(-int(tok[g, i]) // bs)]]
+            mine = [int(x) for i in range(B) for x in tab[g, i, :-(-int(tok[g, i]) // bs)]]
+            assert mine == [f - flat[0] for f in flat]          # compact pools: arrival order
 
 
 def test_page_placer_policies():
