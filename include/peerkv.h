@@ -201,6 +201,30 @@ int pkv_split_block_table(int device, const int32_t* block_table, int64_t block_
                           int32_t* const* out_tables, int64_t out_stride,
                           int32_t* const* out_lens, void* stream);
 
+/* Appends new tokens' K and V (key / value [n_tokens, n_kv_heads, 128], 16-bit, rows
+ * kv_token_stride elements apart) to a KV cache whose blocks are spread over n_dev GPUs:
+ * slot_mapping[t] = block id * block_size + offset (negative = padding, skipped); block id
+ * g belongs to the GPU d with the largest bases[d] <= g, at local block g - bases[d] (the
+ * reference's peer_base rule, umallm/peerkv/paged.py:52-61, for N GPUs).  Runs on `device`,
+ * which holds key, value and slot_mapping; k_pools[d] / v_pools[d] (host arrays of n_dev
+ * device pointers, element strides per pool) may point into other GPUs' memory (P2P
+ * mapped), so the append needs no second stream.  A slot outside every pool is skipped
+ * and sets PKV_ST_BAD_PAGE in *status_word (a device word of `device`, may be NULL).
+ * This is the write side that the reference lists as missing for its sharded path
+ * (umallm/peerkv/register.py:21-27); it replaces vLLM's reshape_and_cache for such a
+ * cache. */
+/* Lets kernels running on `device` load from and store to `peer_device`'s memory (a
+ * no-op when already enabled or when both are the same GPU).  pkv_exchange_attach does
+ * this for its two devices; callers that hand P2P pool pointers to pkv_kv_append or
+ * pkv_split_block_table without an exchange call it themselves. */
+int pkv_enable_peer_access(int device, int peer_device);
+int pkv_kv_append(int device, const void* key, const void* value, int64_t kv_token_stride,
+                  const int64_t* slot_mapping, int32_t n_tokens, int32_t n_kv_heads,
+                  int32_t head_dim, int32_t block_size, int32_t n_dev, const int64_t* bases,
+                  const int64_t* n_blocks, void* const* k_pools, void* const* v_pools,
+                  const int64_t* page_strides, const int64_t* token_strides,
+                  const int64_t* head_strides, uint32_t* status_word, void* stream);
+
 /* ---- several GPUs ------------------------------------------------------- */
 
 /* Mailboxes of one GPU, allocated once: a q inbox with one epoch tag per sequence, and

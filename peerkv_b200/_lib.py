@@ -22,7 +22,8 @@ EXPORTS = [
     "pkv_home_publish_q", "pkv_home_step", "pkv_peer_step", "pkv_home_partial", "pkv_home_merge",
     "pkv_static_status", "pkv_shard_trace", "pkv_exchange_resync", "pkv_exchange_capture_begin",
     "pkv_exchange_capture_end", "pkv_exchange_replayed",
-    "pkv_add_rmsnorm", "pkv_rope_append", "pkv_swiglu",
+    "pkv_add_rmsnorm", "pkv_rope_append", "pkv_swiglu", "pkv_kv_append",
+    "pkv_enable_peer_access",
 ]
 
 
@@ -97,6 +98,9 @@ def lib():
         "pkv_add_rmsnorm": [C.c_int, vp, vp, vp, vp, i32, i32, f32, i32, vp],
         "pkv_rope_append": [C.c_int, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, i64, i64, i64, vp, vp, i32, vp],
         "pkv_swiglu": [C.c_int, vp, vp, i32, i32, i32, vp],
+        "pkv_enable_peer_access": [C.c_int, C.c_int],
+        "pkv_kv_append": [C.c_int, vp, vp, i64, vp, i32, i32, i32, i32, i32, P(i64), P(i64), P(vp), P(vp),
+                          P(i64), P(i64), P(i64), vp, vp],
     }
     for name, args in sig.items():
         fn = getattr(L, name)

@@ -594,6 +594,59 @@ int pkv_split_block_table(int device, const int32_t* block_table, int64_t block_
   return PKV_OK;
 }
 
+int pkv_enable_peer_access(int device, int peer_device) {
+  if (device == peer_device) return PKV_OK;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", device);
+  int can = 0;
+  PKV_CUDA(cudaDeviceCanAccessPeer(&can, device, peer_device));
+  if (!can) return fail(PKV_E_UNSUPPORTED, "device %d cannot access device %d", device, peer_device);
+  cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+  else if (e != cudaSuccess)
+    return fail(PKV_E_CUDA, "cudaDeviceEnablePeerAccess(%d): %s", peer_device, cudaGetErrorString(e));
+  return PKV_OK;
+}
+
+int pkv_kv_append(int device, const void* key, const void* value, int64_t kv_token_stride,
+                  const int64_t* slot_mapping, int32_t n_tokens, int32_t n_kv_heads, int32_t head_dim,
+                  int32_t block_size, int32_t n_dev, const int64_t* bases, const int64_t* n_blocks,
+                  void* const* k_pools, void* const* v_pools, const int64_t* page_strides,
+                  const int64_t* token_strides, const int64_t* head_strides, uint32_t* status_word,
+                  void* stream) {
+  if (!key || !value || !slot_mapping || !bases || !n_blocks || !k_pools || !v_pools || !page_strides ||
+      !token_strides || !head_strides)
+    return fail(PKV_E_INVALID, "null pointer");
+  if (head_dim != pkv::kHeadDim) return fail(PKV_E_UNSUPPORTED, "head_dim %d: 128 required", head_dim);
+  if (n_dev < 1 || n_dev > pkv::kMaxWorld) return fail(PKV_E_INVALID, "n_dev %d", n_dev);
+  if (n_tokens < 0 || n_kv_heads <= 0 || block_size <= 0)
+    return fail(PKV_E_INVALID, "n_tokens %d n_kv_heads %d block_size %d", n_tokens, n_kv_heads, block_size);
+  if (kv_token_stride % 4 || ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value)) & 7))
+    return fail(PKV_E_INVALID, "key / value rows must be 8-byte aligned");
+  if (n_tokens == 0) return PKV_OK;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", device);
+  pkv::AppendParams p;
+  memset(&p, 0, sizeof p);
+  p.key = key; p.value = value; p.slot_mapping = slot_mapping; p.kv_token_stride = kv_token_stride;
+  p.n_tokens = n_tokens; p.n_kv_heads = n_kv_heads; p.block_size = block_size; p.n_dev = n_dev;
+  p.status = status_word;
+  for (int d = 0; d < n_dev; ++d) {
+    if (!k_pools[d] || !v_pools[d]) return fail(PKV_E_INVALID, "null pool for device %d", d);
+    if (d > 0 && bases[d] < bases[d - 1]) return fail(PKV_E_INVALID, "bases must ascend");
+    if (page_strides[d] % 4 || token_strides[d] % 4 || head_strides[d] % 4 ||
+        ((reinterpret_cast<uintptr_t>(k_pools[d]) | reinterpret_cast<uintptr_t>(v_pools[d])) & 7))
+      return fail(PKV_E_INVALID, "pool %d: strides and bases must keep rows 8-byte aligned", d);
+    p.bases[d] = bases[d]; p.n_blocks[d] = n_blocks[d];
+    p.k_pool[d] = static_cast<uint16_t*>(k_pools[d]); p.v_pool[d] = static_cast<uint16_t*>(v_pools[d]);
+    p.page_stride[d] = page_strides[d]; p.token_stride[d] = token_strides[d]; p.head_stride[d] = head_strides[d];
+  }
+  const int64_t units = (int64_t)n_tokens * n_kv_heads;
+  pkv::kv_append_kernel<<<static_cast<unsigned int>((units + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  PKV_CUDA(cudaGetLastError());
+  return PKV_OK;
+}
+
 }  // extern "C"
 
 // ------------------------------------------------------------------------- //

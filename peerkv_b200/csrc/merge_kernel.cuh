@@ -165,6 +165,53 @@ quantize_kv_kernel(const void* __restrict__ src, int64_t rows, uint8_t* __restri
   if (lane == 0) scales[row] = s16;
 }
 
+// Appends the new tokens' K and V to a KV cache whose blocks are spread over several GPUs
+// (the sharded counterpart of vLLM's reshape_and_cache: slot = block id * block_size +
+// offset).  Runs on the GPU that holds key / value / slot_mapping; the pools of the other
+// GPUs are written through P2P mappings, so the append needs no second stream and is
+// ordered before the step's attention by stream order alone (the query of the step is
+// published to the peers only by a later kernel on the same stream).
+//   owner d of block id g: the largest d with bases[d] <= g; local block = g - bases[d].
+// One warp per (token, kv-head); a negative slot is padding and is skipped.
+struct AppendParams {
+  const void* key;              // [n_tokens][n_kv_heads][128] 16-bit, token stride kv_token_stride
+  const void* value;
+  const int64_t* slot_mapping;  // [n_tokens]
+  int64_t kv_token_stride;      // elements
+  int n_tokens, n_kv_heads, block_size, n_dev;
+  int64_t bases[kMaxWorld];
+  int64_t n_blocks[kMaxWorld];  // blocks of GPU d's pool (ids beyond are skipped and flagged)
+  uint16_t* k_pool[kMaxWorld];  // may be P2P mapped
+  uint16_t* v_pool[kMaxWorld];
+  int64_t page_stride[kMaxWorld], token_stride[kMaxWorld], head_stride[kMaxWorld];   // elements
+  uint32_t* status;             // kStBadPage on a slot outside every pool (may be null)
+};
+
+__global__ void __launch_bounds__(256) kv_append_kernel(const AppendParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (unit >= (int64_t)p.n_tokens * p.n_kv_heads) return;
+  const int tok = (int)(unit / p.n_kv_heads), h = (int)(unit % p.n_kv_heads);
+  const int64_t slot = p.slot_mapping[tok];
+  if (slot < 0) return;
+  const int64_t gid = slot / p.block_size;
+  const int off = (int)(slot - gid * p.block_size);
+  int d = 0;
+  for (int k = 1; k < p.n_dev; ++k) if (gid >= p.bases[k]) d = k;
+  const int64_t local = gid - p.bases[d];
+  if (local < 0 || local >= p.n_blocks[d]) {
+    if (p.status && lane == 0) atomicOr(p.status, kStBadPage);
+    return;
+  }
+  const int64_t src = (int64_t)tok * p.kv_token_stride + (int64_t)h * kHeadDim;
+  const int64_t dst = local * p.page_stride[d] + (int64_t)off * p.token_stride[d] + (int64_t)h * p.head_stride[d];
+  // 128 x 16 bit = 256 bytes per row: 8 bytes per lane
+  const uint2 kv = *(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p.key) + src) + lane);
+  const uint2 vv = *(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p.value) + src) + lane);
+  *(reinterpret_cast<uint2*>(p.k_pool[d] + dst) + lane) = kv;
+  *(reinterpret_cast<uint2*>(p.v_pool[d] + dst) + lane) = vv;
+}
+
 // Splits a global block table into per-GPU local tables (the device-side form of
 // the id test in PeerKV umallm/peerkv/paged.py:52-61, generalised to N GPUs).
 //   mode 0 (ranges):      owner d = largest d with bases[d] <= gid, local id = gid - bases[d]

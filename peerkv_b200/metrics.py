@@ -85,6 +85,7 @@ XFER_BYTES = Counter("peerkv_xfer_bytes_total", "bytes that crossed between GPUs
 # the attention path itself
 ATTN_CALLS = Counter("peerkv_attn_calls_total", "decode-attention calls", ["path"])        # single | sharded | fallback
 KV_BYTES_READ = Counter("peerkv_kv_bytes_read_total", "KV bytes the kernels were asked to read", ["gpu"])
+KV_APPEND_TOKENS = Counter("peerkv_kv_append_tokens_total", "new tokens routed to the GPU that owns their block")
 DEVICE_STATUS = Counter("peerkv_device_status_total", "non-zero device status words read back", ["bit"])
 
 

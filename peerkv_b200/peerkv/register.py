@@ -2,10 +2,10 @@
 seam that routes vLLM's FlashAttention backend to the compute-follows-KV impl, and its
 revert.  Import-safe without vLLM (both functions then return False).
 
-What this does NOT do (nor does the reference, register.py:21-27): make vLLM's block
-manager place a share of each layer's KV pages on the peer GPUs.  Until an allocator
-hands real peer caches to `PeerKVFusedAttentionImpl.set_peer_kv`, every layer falls
-back to the stock kernel.
+Placing a share of each layer's KV pages on the peer GPUs is the other half: see
+kv_alloc.patch_peer_kv_allocation (the reference leaves it open, register.py:21-27).
+Until peer caches reach `PeerKVFusedAttentionImpl.set_peer_kv`, every layer falls back
+to the stock kernel.
 """
 from __future__ import annotations
 
@@ -29,10 +29,10 @@ def install_cfk() -> bool:
         backend = _backend()
         from .vllm_backend import PeerKVFusedAttentionImpl, _HAVE_VLLM
     except Exception as e:  # noqa: BLE001
-        logger.info("PeerKV-CFK: vLLM unavailable (%s); install_cfk() is a no-op.", e)
+        logger.info("sharded decode not installed: vLLM cannot be imported (%s)", e)
         return False
     if not _HAVE_VLLM or backend is None or not hasattr(backend, "get_impl_cls"):
-        logger.warning("PeerKV-CFK: no FlashAttentionBackend.get_impl_cls seam found.")
+        logger.warning("sharded decode not installed: this vLLM has no FlashAttentionBackend.get_impl_cls")
         return False
     orig = backend.__dict__.get("get_impl_cls", None) or backend.get_impl_cls
 
@@ -43,7 +43,7 @@ def install_cfk() -> bool:
     _impl_cls._peerkv_orig = orig  # type: ignore[attr-defined]
     backend.get_impl_cls = patched
     _DONE = True
-    logger.info("PeerKV-CFK: FlashAttentionBackend.get_impl_cls -> PeerKVFusedAttentionImpl")
+    logger.info("sharded decode installed: FlashAttention layers now build PeerKVFusedAttentionImpl")
     return True
 
 

@@ -22,6 +22,7 @@ import os
 
 import torch
 
+from .. import metrics
 from .paged import paged_cfk_decode
 
 logger = logging.getLogger("peerkv.attn")
@@ -89,7 +90,22 @@ class PeerKVFusedAttentionImpl(FlashAttentionImpl):
             logger.warning("PeerKV fused decode declined: %s", e)
             return None
 
-    # --- vLLM hook ------------------------------------------------------------ #
+    # --- vLLM hooks ----------------------------------------------------------- #
+    def do_kv_cache_update(self, layer, key, value, kv_cache, slot_mapping):
+        """vLLM calls this before `forward` to store the new tokens' K/V.  With peer caches
+        set, a token whose block lives on a peer GPU must be written there: one library
+        kernel routes every token to its owner (the stock op only knows the local tensor)."""
+        if self._peer_cache is None or kv_cache is None or kv_cache.dim() != 5 \
+                or kv_cache.dtype not in (torch.float16, torch.bfloat16) or key.dtype != kv_cache.dtype:
+            return super().do_kv_cache_update(layer, key, value, kv_cache, slot_mapping)
+        from .kv_alloc import sharded_kv_append
+        peers = self._peer_cache if isinstance(self._peer_cache, (list, tuple)) else [self._peer_cache]
+        bases = self._peer_base if isinstance(self._peer_base, (list, tuple)) else [self._peer_base]
+        n = slot_mapping.shape[0]                     # key / value may be padded beyond it
+        H, D = kv_cache.shape[3], kv_cache.shape[4]
+        sharded_kv_append(key[:n].view(n, H, D), value[:n].view(n, H, D), slot_mapping, kv_cache, peers, bases)
+        metrics.KV_APPEND_TOKENS.inc(n)
+
     def forward(self, layer, query, key, value, kv_cache, attn_metadata, output=None,
                 output_scale=None, output_block_scale=None):
         O = None
@@ -97,9 +113,11 @@ class PeerKVFusedAttentionImpl(FlashAttentionImpl):
             O = self._try_fused(query, kv_cache, attn_metadata)
         if O is None:
             self.fallback_calls += 1
+            metrics.ATTN_CALLS.labels(path="fallback").inc()
             return super().forward(layer, query, key, value, kv_cache, attn_metadata, output,
                                    output_scale, output_block_scale)
         self.fused_calls += 1
+        metrics.ATTN_CALLS.labels(path="sharded").inc()
         if output is not None:
             n = O.shape[0]                                  # rows past n are vLLM's padding
             flat = output if query.dim() != 2 else output.unsqueeze(0)
