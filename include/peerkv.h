@@ -114,6 +114,12 @@ int pkv_shard_destroy(pkv_shard* s);
 /* Reads (and clears) the device status word; synchronises `stream` first. */
 int pkv_shard_status(pkv_shard* s, void* stream, uint32_t* status_out);
 
+/* Cumulative counters of the shard since its creation; synchronises `stream` first.
+ * launches = decode kernels run; units = (16-token tile, kv-head) pairs those kernels
+ * read, so KV bytes read = units * 16 * 128 * 2 * element size.  Feeds the per-call
+ * counters the reference plans (umallm/observability/metrics.py:31-46). */
+int pkv_shard_stats(pkv_shard* s, void* stream, uint64_t* launches_out, uint64_t* units_out);
+
 /* Shard partial in the reference's (O, lse) convention
  * (umallm/peer_parallel_attn.py:46-71): o_part [batch, n_q_heads, 128] fp32,
  * normalised; lse_part [batch, n_q_heads] fp32, natural log; an empty shard
@@ -213,6 +219,23 @@ int pkv_split_block_table(int device, const int32_t* block_table, int64_t block_
  * This is the write side that the reference lists as missing for its sharded path
  * (umallm/peerkv/register.py:21-27); it replaces vLLM's reshape_and_cache for such a
  * cache. */
+/* Attention partial for MANY query rows over one contiguous KV shard (sharded prefill):
+ * q (batch, n_q_heads, sq, 128), k / v (batch, n_kv_heads, sk, 128), 16-bit, element
+ * strides given (multiples of 8, unit last stride).  With causal != 0 query row i sees key
+ * j iff k_pos0 + j <= q_pos0 + i (the diagonal of a ring: q_pos0 == k_pos0); otherwise
+ * every key.  o_part [batch, n_q_heads, sq, 128] fp32 normalised, lse_part [batch,
+ * n_q_heads, sq] natural log, -inf and O = 0 for a row that sees no key: the convention of
+ * pkv_decode_partial, so pkv_merge_partials merges shards.  The shard is read once per
+ * 64 query rows and head.  Replaces the aten flash-attention calls of
+ * umallm/peer_parallel_attn.py:60-66 (flash_partial) and :95-101 (_causal_partial). */
+int pkv_prefill_partial(int device, const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                        int64_t q_stride_s, const void* k, const void* v, int64_t kv_stride_b,
+                        int64_t kv_stride_h, int64_t kv_stride_s, int32_t batch,
+                        int32_t n_q_heads, int32_t n_kv_heads, int32_t sq, int32_t sk,
+                        int32_t head_dim, int32_t dtype, float scale, int32_t causal,
+                        int64_t q_pos0, int64_t k_pos0, float* o_part, float* lse_part,
+                        void* stream);
+
 /* Lets kernels running on `device` load from and store to `peer_device`'s memory (a
  * no-op when already enabled or when both are the same GPU).  pkv_exchange_attach does
  * this for its two devices; callers that hand P2P pool pointers to pkv_kv_append or

@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libpeerkv.so")
 SOURCES = ["api.cu"]
-HEADERS = ["ptx.cuh", "decode_kernel.cuh", "merge_kernel.cuh", "layer_kernels.cuh", os.path.join("..", "..", "include", "peerkv.h")]
+HEADERS = ["ptx.cuh", "decode_kernel.cuh", "merge_kernel.cuh", "layer_kernels.cuh", "prefill_kernel.cuh", os.path.join("..", "..", "include", "peerkv.h")]
 
 
 def _nvcc() -> str:

@@ -3,6 +3,7 @@
 // event creation happens on the per-step entry points.
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <cstdarg>
 #include <cstdio>
@@ -14,6 +15,7 @@
 #include "../../include/peerkv.h"
 #include "merge_kernel.cuh"
 #include "layer_kernels.cuh"
+#include "prefill_kernel.cuh"
 
 namespace {
 
@@ -36,6 +38,13 @@ int fail(int code, const char* fmt, ...) {
       return fail(PKV_E_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_),   \
                   __FILE__, __LINE__);                                                  \
   } while (0)
+
+// A named range around each entry point's work, for timelines taken with a profiler
+// (header-only NVTX: costs a few nanoseconds when nothing listens).
+struct Range {
+  explicit Range(const char* name) { nvtxRangePushA(name); }
+  ~Range() { nvtxRangePop(); }
+};
 
 struct DeviceGuard {
   int prev = -1;
@@ -333,6 +342,7 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   p.part_tags = lo.part_tags;
   p.force_empty = kv.n_pages > 0 ? 0 : 1;
   p.trace = s->trace;
+  p.stats = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(s->status) + 64);
   p.k_scale = kv.k_scale;
   p.v_scale = kv.v_scale;
   p.fuse = lo.skip_combine ? 0 : 1;
@@ -370,6 +380,7 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
     }
   }
 
+  Range range(lo.home ? "pkv:home_step(publish+partial+merge)" : lo.q_tags ? "pkv:peer_step(partial)" : "pkv:decode");
   // An empty pool goes through the same kernel: every sequence counts as empty, no tile is
   // ever loaded (the zeroed tensor maps are not touched), and the service warps write the
   // neutral rows (O = 0, lse = -inf) or, on the home GPU, the merge of the peers' rows.
@@ -493,6 +504,19 @@ int pkv_shard_status(pkv_shard* s, void* stream, uint32_t* status_out) {
   return PKV_OK;
 }
 
+int pkv_shard_stats(pkv_shard* s, void* stream, uint64_t* launches_out, uint64_t* units_out) {
+  if (!s) return fail(PKV_E_INVALID, "null shard");
+  DeviceGuard guard(s->device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", s->device);
+  unsigned long long v[2] = {0, 0};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  PKV_CUDA(cudaMemcpyAsync(v, reinterpret_cast<uint8_t*>(s->status) + 64, sizeof v, cudaMemcpyDeviceToHost, st));
+  PKV_CUDA(cudaStreamSynchronize(st));
+  if (launches_out) *launches_out = v[0];
+  if (units_out) *units_out = v[1];
+  return PKV_OK;
+}
+
 int pkv_decode_partial(pkv_shard* s, const pkv_decode_args* a, float* o_part, float* lse_part,
                        void* stream) {
   if (!o_part || !lse_part) return fail(PKV_E_INVALID, "null o_part or lse_part");
@@ -538,6 +562,7 @@ int pkv_merge_partials(int device, const float* o_parts, int64_t o_part_stride,
   m.o_stride = o_part_stride; m.lse_stride = lse_part_stride;
   m.n_parts = n_parts; m.rows = rows;
   m.out = out; m.out_dtype = out_dtype; m.lse_out = lse_out;
+  Range range("pkv:merge");
   pkv::merge_partials_kernel<<<(rows + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(m);
   PKV_CUDA(cudaGetLastError());
   return PKV_OK;
@@ -590,6 +615,49 @@ int pkv_split_block_table(int device, const int32_t* block_table, int64_t block_
     p.out_lens[d] = out_lens[d];
   }
   pkv::split_block_table_kernel<<<dim3(batch, n_dev), 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  PKV_CUDA(cudaGetLastError());
+  return PKV_OK;
+}
+
+int pkv_prefill_partial(int device, const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                        const void* k, const void* v, int64_t kv_stride_b, int64_t kv_stride_h,
+                        int64_t kv_stride_s, int32_t batch, int32_t n_q_heads, int32_t n_kv_heads, int32_t sq,
+                        int32_t sk, int32_t head_dim, int32_t dtype, float scale, int32_t causal,
+                        int64_t q_pos0, int64_t k_pos0, float* o_part, float* lse_part, void* stream) {
+  if (!q || !o_part || !lse_part) return fail(PKV_E_INVALID, "null pointer");
+  if (head_dim != pkv::kHeadDim) return fail(PKV_E_UNSUPPORTED, "head_dim %d: the kernels require 128", head_dim);
+  if (!is_16bit(dtype)) return fail(PKV_E_INVALID, "dtype must be PKV_F16 or PKV_BF16");
+  if (batch < 0 || sq < 0 || sk < 0 || n_kv_heads <= 0 || n_q_heads <= 0 || n_q_heads % n_kv_heads)
+    return fail(PKV_E_INVALID, "batch %d sq %d sk %d heads %d/%d", batch, sq, sk, n_q_heads, n_kv_heads);
+  if (batch > 65535 || n_q_heads > 65535) return fail(PKV_E_UNSUPPORTED, "batch and heads must fit a grid dimension");
+  if (sk > 0 && (!k || !v)) return fail(PKV_E_INVALID, "null k or v");
+  if ((q_stride_b | q_stride_h | q_stride_s | kv_stride_b | kv_stride_h | kv_stride_s) % 8)
+    return fail(PKV_E_INVALID, "strides must be multiples of 8 elements (16 bytes)");
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15)
+    return fail(PKV_E_INVALID, "q, k and v must be 16-byte aligned");
+  if (batch == 0 || sq == 0) return PKV_OK;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", device);
+  static bool attr_done[64] = {};
+  if (device < 64 && !attr_done[device]) {
+    PKV_CUDA(cudaFuncSetAttribute(pkv::prefill_partial_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, pkv::kPfSmem));
+    PKV_CUDA(cudaFuncSetAttribute(pkv::prefill_partial_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, pkv::kPfSmem));
+    attr_done[device] = true;
+  }
+  pkv::PrefillParams p;
+  memset(&p, 0, sizeof p);
+  p.q = q; p.k = k; p.v = v;
+  p.q_sb = q_stride_b; p.q_sh = q_stride_h; p.q_ss = q_stride_s;
+  p.kv_sb = kv_stride_b; p.kv_sh = kv_stride_h; p.kv_ss = kv_stride_s;
+  p.n_q_heads = n_q_heads; p.group = n_q_heads / n_kv_heads; p.sq = sq; p.sk = sk;
+  p.causal = causal ? 1 : 0; p.q_pos0 = q_pos0; p.k_pos0 = k_pos0;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.o_part = o_part; p.lse_part = lse_part;
+  Range range("pkv:prefill_partial");
+  const dim3 grid((sq + pkv::kPfRows - 1) / pkv::kPfRows, n_q_heads, batch);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == PKV_BF16) pkv::prefill_partial_kernel<true><<<grid, pkv::kPfThreads, pkv::kPfSmem, st>>>(p);
+  else                   pkv::prefill_partial_kernel<false><<<grid, pkv::kPfThreads, pkv::kPfSmem, st>>>(p);
   PKV_CUDA(cudaGetLastError());
   return PKV_OK;
 }
@@ -829,6 +897,7 @@ int pkv_home_publish_q(pkv_exchange* x, const void* q, int32_t batch, void* stre
   if (n > 0) {
     DeviceGuard guard(x->device);
     if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", x->device);
+    Range range("pkv:publish_q");
     pkv::publish_q_kernel<<<n, 1024, 0, static_cast<cudaStream_t>(stream)>>>(p);
     PKV_CUDA(cudaGetLastError());
   }
@@ -919,6 +988,7 @@ int pkv_home_merge(pkv_exchange* x, int32_t batch, uint32_t wait_mask, void* out
   m.epoch_rel = x->epoch - x->base_host;
   m.timeout_ns = kWaitNs;
   m.status = x->status;
+  Range range("pkv:home_merge(wait+merge)");
   pkv::merge_partials_kernel<<<(m.rows + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(m);
   PKV_CUDA(cudaGetLastError());
   return PKV_OK;

@@ -117,6 +117,8 @@ struct DecodeParams {
   int64_t mg_o_stride, mg_lse_stride, mg_tag_stride;
   uint64_t mg_timeout_ns;
   uint32_t* mg_status;         // the exchange's status word
+  // cumulative counters of the shard: [0] launches, [1] (16-token tile, kv-head) units read; or null
+  unsigned long long* stats;
   // measurement aid: [CTAs][kTraceWords] %globaltimer stamps, or null
   //   0 CTA start   1 q published (home) / first q tag seen (peer)   2 last tile consumed
   //   3 last local combine done   4 last peer tag seen (home)   5 last row written
@@ -607,6 +609,10 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
   // late) plus two seconds
   const unsigned long long pipe_deadline = t_start + p.q_timeout_ns + 2000000000ull;
   if (threadIdx.x == 0) trace_first(p, 0);
+  if (p.stats && threadIdx.x == 0 && blockIdx.x == 0) {
+    if (blockIdx.y == 0) atomicAdd(p.stats, 1ull);
+    atomicAdd(p.stats + 1, (unsigned long long)total * (unsigned long long)heads_here);   // (tile, kv-head) units
+  }
   if (p.obs_write && warp == 0 && lane == 0 && blockIdx.y == 0) {
     if (blockIdx.x == 0) p.obs_write[0] = (uint32_t)p.n_cta_x;
     if (g0 >= g1) {                       // nothing to time: keep the weight, no rate

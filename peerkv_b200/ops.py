@@ -61,6 +61,18 @@ class Shard:
         check(_lib.lib().pkv_shard_status(self._h, _stream(self.device), C.byref(v)))
         return int(v.value)
 
+    def stats(self, element_size: int = 2) -> dict:
+        """Cumulative launches and KV bytes read by this shard's kernels (synchronises);
+        also adds what is new since the last call to the package's counters."""
+        from . import metrics
+        a, b = C.c_uint64(), C.c_uint64()
+        check(_lib.lib().pkv_shard_stats(self._h, _stream(self.device), C.byref(a), C.byref(b)))
+        kv_bytes = int(b.value) * 16 * HEAD_DIM * 2 * element_size
+        new = kv_bytes - getattr(self, "_bytes_seen", 0)
+        self._bytes_seen = kv_bytes
+        metrics.KV_BYTES_READ.labels(gpu=self.device.index).inc(new)
+        return {"launches": int(a.value), "kv_bytes_read": kv_bytes}
+
     def raise_on_status(self):
         st = self.status()
         if st:
@@ -70,19 +82,28 @@ class Shard:
 
 
 _shards = {}
+_retired = []          # (shard, event): outgrown contexts whose scratch queued kernels may still use
 
 
 def get_shard(device: torch.device, batch: int, n_q_heads: int) -> Shard:
-    """Cached per (device, n_q_heads); regrown when a larger batch shows up."""
+    """Cached per (device, n_q_heads); regrown when a larger batch shows up.  The outgrown
+    context is not freed under kernels that may still be queued on it, and the host does
+    not wait for them either: it is retired with an event and freed once that has passed."""
     device = torch.device(device)
     if device.index is None:
         device = torch.device("cuda", torch.cuda.current_device())
     key = (device.index, n_q_heads)
+    for item in list(_retired):
+        if item[1].query():
+            item[0].close()
+            _retired.remove(item)
     s = _shards.get(key)
     if s is None or s.max_batch < batch:
         if s is not None:
-            torch.cuda.synchronize(device)
-            s.close()
+            ev = torch.cuda.Event()
+            with torch.cuda.device(device):
+                ev.record(torch.cuda.current_stream(device))
+            _retired.append((s, ev))
         cap = min(4096, max(64, 1 << max(0, batch - 1).bit_length()))   # next power of two, 64..4096
         s = Shard(device, max(cap, batch), n_q_heads)                    # > 4096: let the library refuse it
         _shards[key] = s

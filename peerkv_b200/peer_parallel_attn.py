@@ -32,57 +32,56 @@ def _rows(q):
     return q.permute(0, 2, 1, 3).reshape(B * Lq, H, D), B, Lq
 
 
-def _decode_partial_rows(q_rows, K, V, row_page, row_len, scale):
-    """The one call into the library that this module makes for a shard: every row of
-    q_rows [R, H, D] is a "sequence" that attends to the first row_len[r] tokens of page
-    row_page[r] of the contiguous K/V (B, Hkv, T, D) (one page per batch element).
-    Returns fp32 (O [R, H, D], lse [R, H])."""
+def _prefill_partial(q, K, V, scale, causal, q_pos0=0, k_pos0=0):
+    """The one call into the library for a shard with several query rows: q (B,H,Lq,D),
+    K/V (B,Hkv,Tk,D) on the same GPU -> fp32 (O (B,H,Lq,D), lse (B,H,Lq)).  With `causal`
+    query row i sees key j iff k_pos0 + j <= q_pos0 + i."""
     import ctypes as C
     import torch
     from . import _lib
-    R, H, D = q_rows.shape
-    o = torch.empty(R, H, D, dtype=torch.float32, device=q_rows.device)
-    lse = torch.empty(R, H, dtype=torch.float32, device=q_rows.device)
-    view = ops.contiguous_view(K, V)
-    step = 4096                                    # rows per launch (the shard scratch's batch limit)
-    for r0 in range(0, R, step):
-        r1 = min(R, r0 + step)
-        qs = ops._check_q(q_rows[r0:r1])
-        bt = row_page[r0:r1].to(torch.int32).contiguous().view(-1, 1)
-        sl = row_len[r0:r1].to(torch.int32).contiguous()
-        a = ops.make_args(qs, view, bt, 1, sl, scale)
-        shard = ops.get_shard(q_rows.device, r1 - r0, H)
-        _lib.check(_lib.lib().pkv_decode_partial(shard._h, C.byref(a), o[r0:r1].data_ptr(),
-                                                 lse[r0:r1].data_ptr(), ops._stream(q_rows.device)))
+
+    def strided(t):
+        ok = t.numel() == 0 or (t.stride(3) == 1 and all(st % 8 == 0 for st in t.stride()[:3]) and t.data_ptr() % 16 == 0)
+        return t if ok else t.contiguous()
+    q, K, V = strided(q), strided(K), strided(V)
+    if K.stride() != V.stride():
+        K, V = K.contiguous(), V.contiguous()
+    B, H, Lq, D = q.shape
+    Hkv, Tk = K.shape[1], K.shape[2]
+    o = torch.empty(B, H, Lq, D, dtype=torch.float32, device=q.device)
+    lse = torch.empty(B, H, Lq, dtype=torch.float32, device=q.device)
+    _lib.check(_lib.lib().pkv_prefill_partial(
+        q.device.index, q.data_ptr(), q.stride(0), q.stride(1), q.stride(2),
+        K.data_ptr() if Tk else None, V.data_ptr() if Tk else None, K.stride(0), K.stride(1), K.stride(2),
+        B, H, Hkv, Lq, Tk, D, ops._DT[q.dtype], float(scale), 1 if causal else 0, int(q_pos0), int(k_pos0),
+        o.data_ptr(), lse.data_ptr(), ops._stream(q.device)))
     return o, lse
 
 
 def _partial_f32(q, K, V, scale, causal_diagonal=False):
     """fp32 (O (B,H,Lq,D), lse (B,H,Lq)) of one shard on K's device.  With
-    causal_diagonal, query position p of the shard sees keys 0..p of the same shard."""
-    import torch
+    causal_diagonal, query position p of the shard sees keys 0..p of the same shard.
+    One query row per sequence is the decode kernel's case; more rows go to the prefill
+    kernel, which reads the shard once per 64 rows instead of once per row."""
     if K.dim() != 4 or K.shape != V.shape:
         raise PeerKVError("K and V must both be (B, Hkv, Tk, D)")
     if K.dtype != q.dtype:
         raise PeerKVError(f"q ({q.dtype}) and K ({K.dtype}) must share a dtype")
-    qr, B, Lq = _rows(q)
-    H, D = qr.shape[1], qr.shape[2]
+    if q.dim() != 4:
+        raise PeerKVError(f"q must be (B, H, Lq, D); got {tuple(q.shape)}")
+    ops._require_cuda(q, "q")
+    ops._same_gpu(K, q.device, "K"); ops._same_gpu(V, q.device, "V")
+    B, H, Lq, D = q.shape
+    if D != ops.HEAD_DIM or q.dtype not in (__import__("torch").float16, __import__("torch").bfloat16):
+        raise PeerKVError(f"q must be fp16 or bf16 with D = {ops.HEAD_DIM}")
     Tk = K.shape[2]
-    if Lq == 1 and not causal_diagonal:
+    if causal_diagonal and Lq != Tk:
+        raise PeerKVError("the causal diagonal needs as many queries as keys in the shard")
+    if Lq == 1:                                   # causal or not, one row sees the whole shard
+        qr, _, _ = _rows(q)
         o, lse = ops.partial_contiguous(qr, K, V, scale)
-    else:
-        # every query position is its own "sequence" over its batch element's KV page
-        row_page = torch.arange(B, device=q.device).repeat_interleave(Lq)
-        if causal_diagonal:
-            if Lq != Tk:
-                raise PeerKVError("the causal diagonal needs as many queries as keys in the shard")
-            row_len = torch.arange(1, Lq + 1, device=q.device).repeat(B)
-        else:
-            row_len = torch.full((B * Lq,), Tk, device=q.device)
-        o, lse = _decode_partial_rows(qr, K, V, row_page, row_len, scale)
-    o = o.view(B, Lq, H, D).permute(0, 2, 1, 3)
-    lse = lse.view(B, Lq, H).permute(0, 2, 1)
-    return o, lse
+        return o.view(B, 1, H, D).permute(0, 2, 1, 3), lse.view(B, 1, H).permute(0, 2, 1)
+    return _prefill_partial(q, K, V, scale, causal_diagonal)
 
 
 def flash_partial(q, K, V, scale=None):
@@ -116,6 +115,26 @@ def peer_parallel_attention(q, kv_shards, scale=None):
         scale = 1.0 / (q.shape[-1] ** 0.5)
     B, H, Lq, D = q.shape
     N = len(kv_shards)
+    shard_devs = [K.device for K, _ in kv_shards]
+    if Lq == 1 and q.is_cuda and any(d != dev for d in shard_devs) \
+            and len({d.index for d in shard_devs}) == N and all(d.type == "cuda" for d in shard_devs):
+        # Decode with one shard per GPU: the group's protocol -- q pushed into the peers'
+        # inboxes by the home kernel, every peer's partial stored straight into the home
+        # GPU's slot, merged in the home kernel's tail.  No copy_, no separate merge launch.
+        from .group import group_for
+        others = [d for d in shard_devs if d != dev]
+        grp = group_for([dev] + others, B, H)
+        by_dev = {d.index: kv for d, kv in zip(shard_devs, kv_shards)}
+        K0 = kv_shards[0][0]
+        ordered = []
+        for d in grp.devices:
+            if d.index in by_dev:
+                ordered.append(by_dev[d.index])
+            else:                                   # nothing of the KV lives with the query
+                z = torch.empty(B, K0.shape[1], 0, D, dtype=q.dtype, device=d)
+                ordered.append((z, z))
+        out = grp.decode_contiguous(q[:, :, 0], ordered, scale)
+        return out.view(B, H, 1, D)
     o_all = torch.empty(N, B, H, Lq, D, dtype=torch.float32, device=dev)
     l_all = torch.empty(N, B, H, Lq, dtype=torch.float32, device=dev)
     remote = []
@@ -144,9 +163,9 @@ def ring_prefill_attention(shards, scale=None):
     shards in full and to its own shard causally; as in the reference the earlier shards'
     KV is copied to the later GPU for that.  Returns the outputs O_i on each shard's GPU.
 
-    Built from the decode kernel: a query row is a one-token "sequence" whose length is
-    the number of keys it may see, so causality needs no mask.  This reads the shard's KV
-    once per query row -- fine for checking a sharded prefill, not a prefill kernel.
+    Every (query shard, key shard) pair is one launch of the prefill kernel
+    (`pkv_prefill_partial`: 64 query rows per CTA stream the key shard once; the diagonal
+    pair is causal), and one merge per query shard folds the partials.
     """
     import torch
     if scale is None:

@@ -54,7 +54,9 @@ def simulate(lens, page_size, n_cta, wph, bound_fn):
     grp_slot0 = (n_cta + B) * MAX_WPH
     n_slots = grp_slot0 + (n_cta + GROUP_CTAS - 1) // GROUP_CTAS + B
     covered = [0] * total
-    flushes = {}            # seq -> list of (cta, parity, slot)
+    sib_slot0 = grp_slot0 // MAX_WPH          # where the second warp of a head parks its partial
+    flushes = {}            # seq -> list of (cta, slot): what the merge of the sequence reads
+    parked = set()
     for c in range(n_cta):
         g0, g1 = bound[c], bound[c + 1]
         g = g0
@@ -63,10 +65,15 @@ def simulate(lens, page_size, n_cta, wph, bound_fn):
             seg_end = min(g1, prefix[s + 1])
             for t in range(g, seg_end):
                 covered[t] += 1
-            for par in range(wph):
-                slot = (c + s) * wph + par
-                assert 0 <= slot < grp_slot0
-                flushes.setdefault(s, []).append((c, par, slot))
+            # with two warps per head the second one parks its partial in a slot of its own,
+            # the first folds it in: ONE slot per (CTA, sequence) reaches the merge either way
+            slot = c + s
+            assert 0 <= slot < sib_slot0
+            flushes.setdefault(s, []).append((c, slot))
+            if wph > 1:
+                park = sib_slot0 + c + s
+                assert sib_slot0 <= park < grp_slot0 and park not in parked, "parking slots do not collide"
+                parked.add(park)
             g = seg_end
     assert all(x == 1 for x in covered), "every tile is processed exactly once"
     seen_slots, seen_gslots = set(), set()
@@ -76,9 +83,9 @@ def simulate(lens, page_size, n_cta, wph, bound_fn):
             assert s not in flushes
             continue
         c0, c1 = find_cta(bound, t0), find_cta(bound, t1 - 1)
-        assert sorted({c for c, _, _ in flushes[s]}) == list(range(c0, c1 + 1)), "consecutive CTAs, none empty"
-        slot_lo, slot_hi = (c0 + s) * wph, (c1 + s) * wph + wph - 1
-        slots = sorted(sl for _, _, sl in flushes[s])
+        assert sorted({c for c, _ in flushes[s]}) == list(range(c0, c1 + 1)), "consecutive CTAs, none empty"
+        slot_lo, slot_hi = c0 + s, c1 + s
+        slots = sorted(sl for _, sl in flushes[s])
         assert slots == list(range(slot_lo, slot_hi + 1)), "the merge reads exactly the slots that were written"
         assert not (set(slots) & seen_slots), "no slot is shared by two sequences"
         seen_slots |= set(slots)
@@ -88,7 +95,7 @@ def simulate(lens, page_size, n_cta, wph, bound_fn):
             for gi in range(g_lo, g_hi + 1):
                 cg0, cg1 = max(c0, gi * GROUP_CTAS), min(c1, gi * GROUP_CTAS + GROUP_CTAS - 1)
                 members = [f for f in flushes[s] if f[0] // GROUP_CTAS == gi]
-                assert len(members) == (cg1 - cg0 + 1) * wph, "group arrival count"
+                assert len(members) == cg1 - cg0 + 1, "group arrival count"
                 gslot = grp_slot0 + gi + s
                 assert grp_slot0 <= gslot < n_slots and gslot not in seen_gslots
                 seen_gslots.add(gslot)

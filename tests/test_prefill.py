@@ -1,9 +1,10 @@
 """ring_prefill_attention and multi-query partials (reference
 umallm/peer_parallel_attn.py:112-140 and tests/test_peer_parallel.py:63-95).
 
-CPU: the host-side construction (one "sequence" per query row, causality by length) is
-checked against dense causal attention with the CPU oracle standing in for the one
-library call.  GPU: the same entry points on the real kernels."""
+CPU: the host-side construction (which shard pairs are computed, which one is causal,
+what is merged) is checked against dense causal attention with the CPU oracle standing in
+for the per-shard library call.  GPU: the same entry points on the real kernels, and the
+prefill kernel itself against fp32 attention over edge shapes."""
 import pytest
 import torch
 import torch.nn.functional as F
@@ -15,21 +16,23 @@ from oracle import peerkv_oracle as orc
 def oracle_backed(monkeypatch):
     from peerkv_b200 import ops, peer_parallel_attn as ppa
 
-    def fake_rows(q_rows, K, V, row_page, row_len, scale):
-        R, H, D = q_rows.shape
-        o = torch.zeros(R, H, D)
-        l = torch.full((R, H), float("-inf"))
-        for r in range(R):
-            b, n = int(row_page[r]), int(row_len[r])
-            oo, ll = orc.dense_attention_lse_fp32(q_rows[r].view(1, H, 1, D), K[b:b + 1, :, :n], V[b:b + 1, :, :n], scale)
-            o[r], l[r] = oo.view(H, D), ll.view(H)
+    def fake_partial(q, K, V, scale, causal_diagonal=False):
+        """What the library computes for a shard, from the oracle: every key, or keys <= the row."""
+        B, H, Lq, D = q.shape
+        if not causal_diagonal:
+            return orc.dense_attention_lse_fp32(q, K, V, scale)
+        o = torch.zeros(B, H, Lq, D)
+        l = torch.full((B, H, Lq), float("-inf"))
+        for r in range(Lq):
+            oo, ll = orc.dense_attention_lse_fp32(q[:, :, r:r + 1], K[:, :, :r + 1], V[:, :, :r + 1], scale)
+            o[:, :, r], l[:, :, r] = oo[:, :, 0], ll[:, :, 0]
         return o, l
 
     def fake_merge(o_parts, lse_parts, out_dtype=torch.float32, return_lse=False):
         O, L = orc.merge_n(list(o_parts), list(lse_parts))
         return (O.to(out_dtype), L) if return_lse else O.to(out_dtype)
 
-    monkeypatch.setattr(ppa, "_decode_partial_rows", fake_rows)
+    monkeypatch.setattr(ppa, "_partial_f32", fake_partial)
     monkeypatch.setattr(ops, "merge_partials", fake_merge)
     return ppa
 
@@ -55,6 +58,41 @@ def test_multi_query_host_logic(oracle_backed):
     o, lse = oracle_backed._partial_f32(q, K, V, 1.0 / 8)
     assert torch.allclose(o, F.scaled_dot_product_attention(q, K, V), atol=1e-5, rtol=1e-4)
     assert lse.shape == (2, 4, 5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("Sq,Sk,causal,qp,kp", [
+    (1, 1, True, 0, 0), (64, 64, True, 0, 0), (65, 65, True, 0, 0), (200, 200, True, 0, 0),
+    (130, 1000, False, 0, 0), (63, 7, False, 0, 0), (300, 300, True, 300, 300),
+    (128, 256, True, 256, 64),          # a later query shard against an earlier, overlapping key range
+    (100, 50, True, 0, 80),             # keys that start after some rows: those rows see nothing
+    (17, 0, False, 0, 0),               # an empty shard
+])
+def test_prefill_partial_kernel(dt, Sq, Sk, causal, qp, kp):
+    """pkv_prefill_partial against fp32 attention with the same visibility rule."""
+    from peerkv_b200 import peer_parallel_attn as ppa
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(Sq * 1000 + Sk)
+    B, H, Hkv, D = 2, 8, 2, 128
+    q = torch.randn(B, H, Sq, D).to(dt)
+    K = torch.randn(B, Hkv, Sk, D).to(dt)
+    V = torch.randn(B, Hkv, Sk, D).to(dt)
+    o, lse = ppa._prefill_partial(q.to(dev), K.to(dev), V.to(dev), 1.0 / D ** 0.5, causal, qp, kp)
+    Ke, Ve = K.float().repeat_interleave(H // Hkv, 1), V.float().repeat_interleave(H // Hkv, 1)
+    s = (q.float() / D ** 0.5) @ Ke.transpose(-1, -2)
+    if causal:
+        vis = (kp + torch.arange(Sk))[None, :] <= (qp + torch.arange(Sq))[:, None]
+        s = s.masked_fill(~vis, float("-inf"))
+    ref_lse = torch.logsumexp(s, dim=-1) if Sk else torch.full((B, H, Sq), float("-inf"))
+    seen = torch.isfinite(ref_lse)
+    w = torch.softmax(s, dim=-1) if Sk else s
+    w = torch.where(seen[..., None], w, torch.zeros_like(w))
+    ref = w @ Ve
+    assert torch.allclose(o.cpu(), ref, atol=2e-3, rtol=1e-2)
+    assert torch.equal(torch.isfinite(lse.cpu()), seen)
+    assert torch.allclose(lse.cpu()[seen], ref_lse[seen], atol=2e-3, rtol=1e-3)
+    assert (o.cpu()[~seen] == 0).all()
 
 
 @pytest.mark.gpu
