@@ -236,6 +236,29 @@ int pkv_prefill_partial(int device, const void* q, int64_t q_stride_b, int64_t q
                         int64_t q_pos0, int64_t k_pos0, float* o_part, float* lse_part,
                         void* stream);
 
+/* Copy-back staging, the fallback when the peers hold KV but may not lend compute
+ * (umallm/vllm_integration/peerkv_staging.py:82-131; chosen under R1-busy,
+ * umallm/elastic_policy.py:346-350).  The home tensor has c_local real blocks followed by
+ * c_scratch scratch blocks.  Every entry of block_table [batch, stride] (global ids, on
+ * `device`) that names a peer block (id >= c_local = bases[1]; GPU d owns ids from
+ * bases[d], n_blocks[d] of them, pools k_pools[d] / v_pools[d] with block stride
+ * page_strides[d] elements, P2P mapped; index 0 unused) is copied into the next free
+ * scratch block -- block_elems elements of elem_size bytes for K and again for V -- and
+ * out_table gets the entry rewritten to that scratch block; local entries are copied
+ * through.  A single-GPU pkv_decode over the home tensor with out_table then gives the
+ * exact result.  scratch_words: `batch` int32 of device scratch.  More peer entries than
+ * scratch blocks, or an id outside every pool, sets PKV_ST_BAD_PAGE in *status_word (a
+ * device word) and leaves that entry pointing at the first scratch block.  No host
+ * synchronisation; the reference's version finds the unique ids on the host. */
+int pkv_stage_peer_blocks(int device, const int32_t* block_table, int64_t block_table_stride,
+                          const int32_t* seq_lens, int32_t batch, int32_t block_size,
+                          int32_t n_dev, const int64_t* bases, const int64_t* n_blocks,
+                          const void* const* k_pools, const void* const* v_pools,
+                          const int64_t* page_strides, void* k_home, void* v_home,
+                          int64_t home_page_stride, int64_t c_local, int64_t c_scratch,
+                          int64_t block_elems, int32_t elem_size, int32_t* out_table,
+                          int32_t* scratch_words, uint32_t* status_word, void* stream);
+
 /* Lets kernels running on `device` load from and store to `peer_device`'s memory (a
  * no-op when already enabled or when both are the same GPU).  pkv_exchange_attach does
  * this for its two devices; callers that hand P2P pool pointers to pkv_kv_append or

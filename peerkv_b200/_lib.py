@@ -23,7 +23,7 @@ EXPORTS = [
     "pkv_static_status", "pkv_shard_trace", "pkv_exchange_resync", "pkv_exchange_capture_begin",
     "pkv_exchange_capture_end", "pkv_exchange_replayed",
     "pkv_add_rmsnorm", "pkv_rope_append", "pkv_swiglu", "pkv_kv_append",
-    "pkv_enable_peer_access", "pkv_shard_stats", "pkv_prefill_partial",
+    "pkv_enable_peer_access", "pkv_shard_stats", "pkv_prefill_partial", "pkv_stage_peer_blocks",
 ]
 
 
@@ -100,6 +100,8 @@ def lib():
         "pkv_swiglu": [C.c_int, vp, vp, i32, i32, i32, vp],
         "pkv_enable_peer_access": [C.c_int, C.c_int],
         "pkv_shard_stats": [vp, vp, P(u64), P(u64)],
+        "pkv_stage_peer_blocks": [C.c_int, vp, i64, vp, i32, i32, i32, P(i64), P(i64), P(vp), P(vp), P(i64), vp, vp,
+                                  i64, i64, i64, i64, i32, vp, vp, vp, vp],
         "pkv_prefill_partial": [C.c_int, vp, i64, i64, i64, vp, vp, i64, i64, i64, i32, i32, i32, i32, i32, i32, i32,
                                 f32, i32, i64, i64, vp, vp, vp],
         "pkv_kv_append": [C.c_int, vp, vp, i64, vp, i32, i32, i32, i32, i32, P(i64), P(i64), P(vp), P(vp),

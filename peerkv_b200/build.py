@@ -56,10 +56,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return LIB
     cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
            "-Xptxas", "-v" if verbose else "-O3", "-shared", "-Xcompiler", "-fPIC",
-           "-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
+           "-o", LIB + ".tmp"] + [os.path.join(CSRC, s) for s in SOURCES]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    os.replace(LIB + ".tmp", LIB)          # never a half-written library in the tree
     with open(STAMP, "w") as f:
         f.write(_source_hash() + "\n")
     if verbose:

@@ -662,6 +662,54 @@ int pkv_prefill_partial(int device, const void* q, int64_t q_stride_b, int64_t q
   return PKV_OK;
 }
 
+int pkv_stage_peer_blocks(int device, const int32_t* block_table, int64_t block_table_stride,
+                          const int32_t* seq_lens, int32_t batch, int32_t block_size, int32_t n_dev,
+                          const int64_t* bases, const int64_t* n_blocks, const void* const* k_pools,
+                          const void* const* v_pools, const int64_t* page_strides, void* k_home, void* v_home,
+                          int64_t home_page_stride, int64_t c_local, int64_t c_scratch, int64_t block_elems,
+                          int32_t elem_size, int32_t* out_table, int32_t* scratch_words, uint32_t* status_word,
+                          void* stream) {
+  if (!block_table || !seq_lens || !bases || !n_blocks || !k_pools || !v_pools || !page_strides || !k_home ||
+      !v_home || !out_table || !scratch_words || !status_word)
+    return fail(PKV_E_INVALID, "null pointer");
+  if (n_dev < 2 || n_dev > pkv::kMaxWorld) return fail(PKV_E_INVALID, "n_dev %d (the home GPU and at least one peer)", n_dev);
+  if (batch < 0 || block_size <= 0 || c_local < 0 || c_scratch < 0 || elem_size <= 0)
+    return fail(PKV_E_INVALID, "batch %d block_size %d c_local %lld c_scratch %lld", batch, block_size,
+                (long long)c_local, (long long)c_scratch);
+  if ((block_elems * elem_size) % 16 || (home_page_stride * elem_size) % 16 ||
+      ((reinterpret_cast<uintptr_t>(k_home) | reinterpret_cast<uintptr_t>(v_home)) & 15))
+    return fail(PKV_E_INVALID, "blocks must be multiples of 16 bytes and 16-byte aligned");
+  if (bases[1] != c_local) return fail(PKV_E_INVALID, "bases[1] must equal c_local");
+  if (batch == 0) return PKV_OK;
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", device);
+  pkv::StageParams p;
+  memset(&p, 0, sizeof p);
+  p.block_table = block_table; p.seq_lens = seq_lens; p.out_table = out_table; p.row_count = scratch_words;
+  p.bt_stride = block_table_stride; p.batch = batch; p.block_size = block_size; p.n_dev = n_dev;
+  p.c_local = c_local; p.c_scratch = c_scratch;
+  for (int d = 0; d < n_dev; ++d) {
+    p.bases[d] = bases[d]; p.n_blocks[d] = n_blocks[d];
+    if (d == 0) continue;
+    if (!k_pools[d] || !v_pools[d]) return fail(PKV_E_INVALID, "null pool for device %d", d);
+    if ((page_strides[d] * elem_size) % 16 ||
+        ((reinterpret_cast<uintptr_t>(k_pools[d]) | reinterpret_cast<uintptr_t>(v_pools[d])) & 15))
+      return fail(PKV_E_INVALID, "pool %d: blocks must be 16-byte aligned", d);
+    p.k_pool[d] = static_cast<const uint4*>(k_pools[d]); p.v_pool[d] = static_cast<const uint4*>(v_pools[d]);
+    p.page_stride16[d] = page_strides[d] * elem_size / 16;
+  }
+  p.k_home = static_cast<uint4*>(k_home); p.v_home = static_cast<uint4*>(v_home);
+  p.home_page_stride16 = home_page_stride * elem_size / 16;
+  p.block_words16 = block_elems * elem_size / 16;
+  p.status = status_word;
+  Range range("pkv:stage_peer_blocks(copy-back)");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  pkv::stage_count_kernel<<<batch, 256, 0, st>>>(p);
+  pkv::stage_copy_kernel<<<batch, 256, 0, st>>>(p);
+  PKV_CUDA(cudaGetLastError());
+  return PKV_OK;
+}
+
 int pkv_enable_peer_access(int device, int peer_device) {
   if (device == peer_device) return PKV_OK;
   DeviceGuard guard(device);

@@ -212,6 +212,122 @@ __global__ void __launch_bounds__(256) kv_append_kernel(const AppendParams p) {
   *(reinterpret_cast<uint2*>(p.v_pool[d] + dst) + lane) = vv;
 }
 
+// Copy-back staging: the fallback when the peers hold KV but may not lend compute
+// (PeerKV umallm/vllm_integration/peerkv_staging.py:82-131, chosen under R1-busy,
+// umallm/elastic_policy.py:346-350).  Every block-table entry that names a peer block is
+// copied over NVLink into a scratch block at the tail of the home GPU's tensor and the
+// entry is rewritten to that scratch block, so a single-GPU decode can run over the
+// home tensor alone.  No host round trip: kernel 1 counts each sequence's peer entries,
+// kernel 2 ranks them (scratch slot = number of peer entries before it, sequence-major)
+// and copies; an entry that finds no scratch slot left is flagged and left pointing at
+// scratch block 0.  A block shared by two sequences is staged twice.
+struct StageParams {
+  const int32_t* block_table;   // [batch][bt_stride] global ids
+  const int32_t* seq_lens;      // [batch]
+  int32_t* out_table;           // [batch][bt_stride] ids into the home tensor (local or scratch)
+  int32_t* row_count;           // [batch] scratch words: peer entries per sequence
+  int64_t bt_stride;
+  int batch, block_size, n_dev;
+  int64_t c_local, c_scratch;   // blocks of the home tensor: [0, c_local) real, then c_scratch scratch blocks
+  int64_t bases[kMaxWorld];     // first id of GPU d's blocks (bases[0] = 0; d >= 1 are the peers)
+  int64_t n_blocks[kMaxWorld];
+  const uint4* k_pool[kMaxWorld];   // peers' pools (P2P mapped); [0] unused
+  const uint4* v_pool[kMaxWorld];
+  int64_t page_stride16[kMaxWorld]; // peers' block strides in 16-byte words
+  uint4* k_home;                // the home tensor (destination)
+  uint4* v_home;
+  int64_t home_page_stride16;
+  int64_t block_words16;        // 16-byte words of one block of K (contiguous inside a block)
+  uint32_t* status;
+};
+
+__global__ void __launch_bounds__(256) stage_count_kernel(const StageParams p) {
+  __shared__ int red[8];
+  const int b = blockIdx.x;
+  const int n_blk = (p.seq_lens[b] + p.block_size - 1) / p.block_size;
+  const int32_t* row = p.block_table + (int64_t)b * p.bt_stride;
+  int cnt = 0;
+  for (int j = threadIdx.x; j < n_blk; j += blockDim.x) cnt += row[j] >= p.c_local ? 1 : 0;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = cnt;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int t = 0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += red[w];
+    p.row_count[b] = t;
+  }
+}
+
+// grid (batch): one block per sequence walks its entries in order, 8 warps = 8 entries at a time.
+__global__ void __launch_bounds__(256) stage_copy_kernel(const StageParams p) {
+  __shared__ int s_base, red[8];
+  const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  {                                                           // peer entries of the sequences before this one
+    int part = 0;
+    for (int i = threadIdx.x; i < b; i += blockDim.x) part += p.row_count[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (lane == 0) red[warp] = part;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int base = 0;
+      for (int w = 0; w < 8; ++w) base += red[w];
+      s_base = base;
+    }
+    __syncthreads();
+  }
+  const int n_blk = (p.seq_lens[b] + p.block_size - 1) / p.block_size;
+  const int32_t* row = p.block_table + (int64_t)b * p.bt_stride;
+  int32_t* out = p.out_table + (int64_t)b * p.bt_stride;
+  int before = s_base;                                        // peer entries ranked so far
+  for (int j0 = 0; j0 < n_blk; j0 += 32) {
+    const int j = j0 + lane;
+    const int64_t gid = j < n_blk ? row[j] : 0;
+    const bool peer = j < n_blk && gid >= p.c_local;
+    const unsigned int bal = __ballot_sync(0xffffffffu, peer);
+    const int slot = before + __popc(bal & ((1u << lane) - 1u));
+    before += __popc(bal);
+    if (j < n_blk && warp == 0) {                              // one warp writes the table
+      int32_t v = (int32_t)gid;
+      if (peer) {
+        if (slot < p.c_scratch) v = (int32_t)(p.c_local + slot);
+        else { v = (int32_t)p.c_local; atomicOr(p.status, kStBadPage); }
+      }
+      out[j] = v;
+    }
+    // the copies: entry e of this group of 32 is taken by warp e mod 8
+    for (int e = warp; e < 32; e += 8) {
+      const bool e_peer = (bal >> e) & 1u;
+      if (!e_peer) continue;
+      const int e_slot = before - __popc(bal) + __popc(bal & ((1u << e) - 1u));
+      if (e_slot >= p.c_scratch) continue;
+      const int64_t e_gid = __shfl_sync(0xffffffffu, gid, e);
+      int d = 1;
+      for (int k = 2; k < p.n_dev; ++k) if (e_gid >= p.bases[k]) d = k;
+      const int64_t local = e_gid - p.bases[d];
+      if (local < 0 || local >= p.n_blocks[d]) { if (lane == 0) atomicOr(p.status, kStBadPage); continue; }
+      const uint4* sk = p.k_pool[d] + local * p.page_stride16[d];
+      const uint4* sv = p.v_pool[d] + local * p.page_stride16[d];
+      uint4* dk = p.k_home + (p.c_local + e_slot) * p.home_page_stride16;
+      uint4* dv = p.v_home + (p.c_local + e_slot) * p.home_page_stride16;
+      for (int64_t i = lane; i < p.block_words16; i += 128) {
+        uint4 a[4], c[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int64_t w = i + 32 * u;
+          if (w < p.block_words16) { a[u] = sk[w]; c[u] = sv[w]; }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int64_t w = i + 32 * u;
+          if (w < p.block_words16) { dk[w] = a[u]; dv[w] = c[u]; }
+        }
+      }
+    }
+  }
+}
+
 // Splits a global block table into per-GPU local tables (the device-side form of
 // the id test in PeerKV umallm/peerkv/paged.py:52-61, generalised to N GPUs).
 //   mode 0 (ranges):      owner d = largest d with bases[d] <= gid, local id = gid - bases[d]

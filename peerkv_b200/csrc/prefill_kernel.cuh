@@ -171,20 +171,32 @@ __global__ void __launch_bounds__(kPfThreads) prefill_partial_kernel(const Prefi
 #pragma unroll
     for (int j = 0; j < 16; ++j) { o[j][0] *= al0; o[j][1] *= al0; o[j][2] *= al1; o[j][3] *= al1; }
 
-    // O += P V : k-step kk covers keys 16kk..16kk+15 = score tiles 2kk, 2kk+1
+    // O += P V : k-step kk covers keys 16kk..16kk+15 = score tiles 2kk, 2kk+1.  A bf16 P
+    // keeps 8 significant bits, which alone would cost up to 2^-9 of the value spread in the
+    // output when a row sees only a few keys; bf16 therefore sends P as two terms (the
+    // rounding and what it left), fp16 (11 bits) as one.
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
-      uint32_t a[4];
-      a[0] = pack2<BF16>(s[2 * kk][0], s[2 * kk][1]);
-      a[1] = pack2<BF16>(s[2 * kk][2], s[2 * kk][3]);
-      a[2] = pack2<BF16>(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-      a[3] = pack2<BF16>(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+      uint32_t a[4], a2[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float x0 = s[2 * kk + (e >> 1)][(e & 1) * 2], x1 = s[2 * kk + (e >> 1)][(e & 1) * 2 + 1];
+        a[e] = pack2<BF16>(x0, x1);
+        if constexpr (BF16) {
+          const float2 r = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a[e]));
+          a2[e] = pack2<true>(x0 - r.x, x1 - r.y);
+        }
+      }
 #pragma unroll
       for (int c = 0; c < 16; c += 2) {
         uint32_t r[4];
         ldmatrix_x4_trans(r, sv_ + pf_off(16 * kk + (lane & 7) + ((lane >> 3) & 1) * 8, c + (lane >> 4)));
         mma_16816<BF16>(o[c], a, r[0], r[1]);
         mma_16816<BF16>(o[c + 1], a, r[2], r[3]);
+        if constexpr (BF16) {
+          mma_16816<true>(o[c], a2, r[0], r[1]);
+          mma_16816<true>(o[c + 1], a2, r[2], r[3]);
+        }
       }
     }
     __syncthreads();          // everyone is done with this stage before it is refilled

@@ -126,11 +126,14 @@ def _enable_peer_access(dev: torch.device, others):
         _peer_enabled.add((dev.index, o.index))
 
 
-def relayout_runner(runner, peer_fraction: float, peer_devices: Sequence[str]) -> List[PeerKVLayout]:
+def relayout_runner(runner, peer_fraction: float, peer_devices: Sequence[str],
+                    scratch_blocks: int = 0) -> List[PeerKVLayout]:
     """Splits every layer's KV tensor of a vLLM model runner (`runner.kv_caches`, each
     [2, num_blocks, bs, H, D] on the home GPU) into a local part and per-peer parts, moves
     the peers' blocks over, replaces the engine's handles by the local part and hands the
-    peer caches to every attention impl that has `set_peer_kv`."""
+    peer caches to every attention impl that has `set_peer_kv`.  With scratch_blocks > 0 the
+    local part gets that many extra blocks at its tail: the staging area of the copy-back
+    corner (staging.PeerKVStager), which the impl uses when the peers may not compute."""
     kv_caches = getattr(runner, "kv_caches", None)
     if not kv_caches:
         raise PeerKVError("runner.kv_caches not found")
@@ -142,13 +145,17 @@ def relayout_runner(runner, peer_fraction: float, peer_devices: Sequence[str]) -
         _, nb, bs, H, D = kv.shape
         lay = PeerKVLayout.split(nb, bs, H, D, peer_fraction, kv.device, peer_devices)
         local, peers = alloc_split_kv(lay, kv.dtype)
-        local.copy_(kv[:, :lay.c_local])
+        if scratch_blocks > 0:
+            local = torch.empty(2, lay.c_local + scratch_blocks, bs, H, D, dtype=kv.dtype, device=kv.device)
+        local[:, :lay.c_local].copy_(kv[:, :lay.c_local])
         for base, c, pk in zip(lay.peer_bases, lay.c_peers, peers):
             pk.copy_(kv[:, base:base + c])
         kv_caches[li] = local
         if li < len(impls):
             mod, impl = impls[li]
             impl.set_peer_kv(peers, lay.peer_bases)
+            if scratch_blocks > 0 and hasattr(impl, "set_scratch"):
+                impl.set_scratch(lay.c_local, scratch_blocks)
             bound = getattr(mod, "kv_cache", None)           # vLLM binds the tensor into the layer too
             if isinstance(bound, list):
                 for i in range(len(bound)):
@@ -194,7 +201,7 @@ def _resolve(spec: str):
 
 
 def patch_peer_kv_allocation(peer_fraction: float = 0.5, peer_devices: Sequence[str] = ("cuda:1",),
-                             target: str = _DEFAULT_TARGET) -> bool:
+                             target: str = _DEFAULT_TARGET, scratch_blocks: int = 0) -> bool:
     """Wraps the runner's `initialize_kv_cache` so that, right after vLLM has allocated
     its KV cache, `peer_fraction` of each layer's blocks move to `peer_devices`.  Call it
     (together with `install_cfk`) before the engine builds its cache.  True if patched."""
@@ -214,7 +221,7 @@ def patch_peer_kv_allocation(peer_fraction: float = 0.5, peer_devices: Sequence[
     def wrapper(self, *args, **kwargs):
         ret = orig(self, *args, **kwargs)
         try:
-            relayout_runner(self, peer_fraction, peer_devices)
+            relayout_runner(self, peer_fraction, peer_devices, scratch_blocks)
         except Exception as e:  # noqa: BLE001 - never break the engine
             logger.error("PeerKV: re-layout failed (%s); the KV cache stays on one GPU", e)
         return ret

@@ -47,7 +47,11 @@ class PeerKVFusedAttentionImpl(FlashAttentionImpl):
         self._peer_base = 1 << 30          # global block id >= this -> peer (or a list of thresholds)
         self._splits = int(os.environ.get("PEERKV_SPLITS", 16))   # accepted for compatibility, unused
         self._scale_override = None
+        self._point = "compute_follows_kv"  # operating point: the sharded path, or "copyback"
+        self._c_local = self._c_scratch = 0
+        self._stager = None
         self.fused_calls = 0
+        self.copyback_calls = 0
         self.fallback_calls = 0
 
     def set_peer_kv(self, peer_cache, peer_base) -> None:
@@ -55,6 +59,16 @@ class PeerKVFusedAttentionImpl(FlashAttentionImpl):
         block-id threshold(s) at/above which blocks live on the peer(s)."""
         self._peer_cache = peer_cache
         self._peer_base = list(peer_base) if isinstance(peer_base, (list, tuple)) else int(peer_base)
+
+    def set_scratch(self, c_local: int, c_scratch: int) -> None:
+        """The allocator tells this layer that its local tensor ends in c_scratch staging blocks."""
+        self._c_local, self._c_scratch = int(c_local), int(c_scratch)
+
+    def set_operating_point(self, point) -> None:
+        """What the policy decided for the running requests (elastic_policy.OperatingPoint or
+        its value): compute-follows-KV on the peers, or copy-back when the peers are busy
+        (umallm/elastic_policy.py:346-350).  Anything else takes the stock kernel."""
+        self._point = getattr(point, "value", point)
 
     # --- the decode fast path ------------------------------------------------ #
     def _try_fused(self, query, kv_cache, attn_metadata):
@@ -84,11 +98,31 @@ class PeerKVFusedAttentionImpl(FlashAttentionImpl):
             if q.dtype not in (torch.float16, torch.bfloat16) or kv_cache.dtype != q.dtype:
                 return None                                # fp8 caches of vLLM use other scales
             scale = self._scale_override or getattr(self, "scale", None) or 1.0 / math.sqrt(D)
+            if self._point == "copyback":
+                return self._copyback(q, kv_cache, bt2, seq_lens[:num_seqs], float(scale))
+            if self._point != "compute_follows_kv":
+                return None
             return paged_cfk_decode(q, kv_cache, self._peer_cache, bt2, seq_lens[:num_seqs],
                                     self._peer_base, scale=float(scale), splits=self._splits)
         except Exception as e:  # noqa: BLE001 - any surprise -> safe fallback
             logger.warning("PeerKV fused decode declined: %s", e)
             return None
+
+    def _copyback(self, q, kv_cache, bt, seq_lens, scale):
+        """Peer blocks staged into the local tensor's scratch tail, then a one-GPU decode."""
+        if self._c_scratch <= 0 or kv_cache.shape[1] != self._c_local + self._c_scratch:
+            return None                                    # no staging area: defer
+        from .staging import PeerKVStager, StagingLayout, copyback_decode
+        peers = self._peer_cache if isinstance(self._peer_cache, (list, tuple)) else [self._peer_cache]
+        if self._stager is None:
+            lay = StagingLayout(self._c_local, self._c_scratch, [p.shape[1] for p in peers], kv_cache.shape[2],
+                                kv_cache.shape[3], kv_cache.shape[4], str(kv_cache.device),
+                                [str(p.device) for p in peers])
+            self._stager = PeerKVStager(lay, max_batch=max(256, bt.shape[0]), max_blocks_per_seq=max(4096, bt.shape[1]))
+        out = copyback_decode(q, kv_cache, peers, bt, seq_lens, self._stager, scale)
+        self.copyback_calls += 1
+        metrics.ATTN_CALLS.labels(path="copyback").inc()
+        return out
 
     # --- vLLM hooks ----------------------------------------------------------- #
     def do_kv_cache_update(self, layer, key, value, kv_cache, slot_mapping):
@@ -116,8 +150,9 @@ class PeerKVFusedAttentionImpl(FlashAttentionImpl):
             metrics.ATTN_CALLS.labels(path="fallback").inc()
             return super().forward(layer, query, key, value, kv_cache, attn_metadata, output,
                                    output_scale, output_block_scale)
-        self.fused_calls += 1
-        metrics.ATTN_CALLS.labels(path="sharded").inc()
+        if self._point == "compute_follows_kv":
+            self.fused_calls += 1
+            metrics.ATTN_CALLS.labels(path="sharded").inc()
         if output is not None:
             n = O.shape[0]                                  # rows past n are vLLM's padding
             flat = output if query.dim() != 2 else output.unsqueeze(0)
