@@ -354,6 +354,7 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   p.grp_counter = s->counters + s->grp_counter_off;
   p.grp_slot0 = s->grp_slot0;
   p.sib_slot0 = s->grp_slot0 / pkv::kMaxWph;
+  p.unit_slot0 = s->n_slots - s->max_batch;
   if (s->obs[0] && n_cta_x <= pkv::kMaxCtas) {
     p.obs_read = s->obs[s->obs_parity];
     p.obs_write = s->obs[s->obs_parity ^ 1];
@@ -452,7 +453,8 @@ int pkv_shard_create(pkv_shard** out, int device, int max_batch, int n_q_heads) 
   s->max_batch = max_batch;
   s->n_q_heads = n_q_heads;
   s->grp_slot0 = (sms + max_batch) * pkv::kMaxWph;                 // per-CTA slots, then per-group slots
-  s->n_slots = s->grp_slot0 + (sms + pkv::kGroupCtas - 1) / pkv::kGroupCtas + max_batch;
+  // ... then per-group slots (CTA group + sequence), then one slot per sequence for the home GPU's own fold
+  s->n_slots = s->grp_slot0 + (sms + pkv::kGroupCtas - 1) / pkv::kGroupCtas + max_batch + max_batch;
   s->maps.reserve(kMapCache);
   const size_t o_bytes = (size_t)s->n_slots * n_q_heads * pkv::kHeadDim * sizeof(float);
   const size_t ml_bytes = (size_t)s->n_slots * n_q_heads * 2 * sizeof(float);
@@ -1060,7 +1062,7 @@ constexpr int kStaticMaxQHeads = 64;
 constexpr int kStaticMaxSms = 192;
 constexpr int kStaticMaxDevices = 16;
 constexpr size_t kStaticGrpSlot0 = (size_t)(kStaticMaxSms + kStaticMaxBatch) * pkv::kMaxWph;
-constexpr size_t kStaticSlots = kStaticGrpSlot0 + kStaticMaxSms / pkv::kGroupCtas + 1 + kStaticMaxBatch;
+constexpr size_t kStaticSlots = kStaticGrpSlot0 + kStaticMaxSms / pkv::kGroupCtas + 1 + 2 * kStaticMaxBatch;
 constexpr size_t kStaticObsWords = 1 + 3 * pkv::kMaxCtas;
 constexpr size_t kStaticGrpOff = 64 + (size_t)kStaticMaxBatch * kStaticMaxQHeads;    // relative to the counters
 constexpr size_t kStaticWords = 64 + kStaticGrpOff +

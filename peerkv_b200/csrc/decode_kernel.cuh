@@ -96,6 +96,7 @@ struct DecodeParams {
   unsigned int* seq_counter;   // [batch][n_kv_heads], zero between launches
   unsigned int* grp_counter;   // [(CTA groups + batch)][n_kv_heads], zero between launches
   int grp_slot0;               // first slot index of the per-group partials
+  int unit_slot0;              // first of the per-sequence slots the home GPU folds its own splits into
   int sib_slot0;               // first slot index of the second warps' parking slots (two warps per head)
   // adaptive split of the tile list: per-CTA (duration ns, tiles, weight) of the previous
   // launch on this shard; written for the next one.  Word 0 is the CTA count they refer to.
@@ -141,6 +142,14 @@ __device__ __forceinline__ void trace_first(const DecodeParams& p, int word) {
   }
 }
 
+// Barrier `id` (1..15) over the first `n` threads' worth of warps; n a multiple of 32.
+__device__ __forceinline__ void bar_sync(int id, int n) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(int id, int n) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(n) : "memory");
+}
+
 // Tiles of a sequence with `len` tokens in this shard.
 __device__ __forceinline__ int seq_tiles(int len, int page_size, int tiles_per_page) {
   int full = len / page_size;
@@ -149,16 +158,18 @@ __device__ __forceinline__ int seq_tiles(int len, int page_size, int tiles_per_p
 }
 
 // Exclusive prefix of tiles per sequence into smem `prefix[0..batch]`.
-// Called by all threads of the block; ends with a __syncthreads().
+// Called by the first `nthr` threads of the block (all but the service warp); ends with
+// a barrier among them.
 __device__ __forceinline__ void build_tile_prefix(int* prefix, const int32_t* seq_lens, int batch,
-                                                  int page_size, int tiles_per_page, bool force_empty) {
-  const int tid = threadIdx.x, nthr = blockDim.x;
+                                                  int page_size, int tiles_per_page, bool force_empty,
+                                                  int nthr) {
+  const int tid = threadIdx.x;
   for (int b = tid; b < batch; b += nthr) {
     int len = force_empty ? 0 : seq_lens[b];
     prefix[b + 1] = len > 0 ? seq_tiles(len, page_size, tiles_per_page) : 0;
   }
   if (tid == 0) prefix[0] = 0;
-  __syncthreads();
+  bar_sync(1, nthr);
   if (tid < 32) {
     int carry = 0;
     for (int base = 1; base <= batch; base += 32) {
@@ -174,7 +185,7 @@ __device__ __forceinline__ void build_tile_prefix(int* prefix, const int32_t* se
       carry = __shfl_sync(0xffffffffu, v, 31);
     }
   }
-  __syncthreads();
+  bar_sync(1, nthr);
 }
 
 // Largest s with prefix[s] <= g (prefix non-decreasing, prefix[batch] > g).
@@ -403,26 +414,27 @@ __device__ __forceinline__ bool pipe_wait(uint32_t bar, uint32_t parity, volatil
 // Each launch therefore records, per CTA, how long its tiles took; the next launch on
 // the same shard splits the list in proportion to those rates (damped, clamped to
 // [0.5, 2]).  Small problems, a first launch, or a changed grid use the equal split, and
-// every CTA computes the same bounds from the same inputs.  Ends with __syncthreads().
+// every CTA computes the same bounds from the same inputs.  Called by the first `nthr`
+// threads of the block; ends with a barrier among them.
 __device__ __forceinline__ void build_cta_bounds(int* bound, float* wtmp, int total, int n_cta,
-                                                 const uint32_t* obs) {
+                                                 const uint32_t* obs, int nthr) {
   const int tid = threadIdx.x;
   const bool adaptive = obs && obs[0] == (uint32_t)n_cta && total >= 8 * n_cta && n_cta <= kMaxCtas;
   if (!adaptive) {
     const int per = (total + n_cta - 1) / n_cta;
-    for (int c = tid; c <= n_cta; c += blockDim.x) {
+    for (int c = tid; c <= n_cta; c += nthr) {
       bound[c] = min(total, c * per);
       if (c < min(n_cta, kMaxCtas)) wtmp[c] = 1.f;
     }
-    __syncthreads();
+    bar_sync(1, nthr);
     return;
   }
   // rates of the previous launch
-  for (int c = tid; c < n_cta; c += blockDim.x) {
+  for (int c = tid; c < n_cta; c += nthr) {
     const float dur = (float)obs[1 + 3 * c], tiles = (float)obs[2 + 3 * c];
     wtmp[c] = (dur > 0.f && tiles > 0.f) ? tiles / dur : 0.f;
   }
-  __syncthreads();
+  bar_sync(1, nthr);
   if (tid < 32) {
     float sum = 0.f; int cnt = 0;
     for (int c = tid; c < n_cta; c += 32) if (wtmp[c] > 0.f) { sum += wtmp[c]; ++cnt; }
@@ -465,7 +477,7 @@ __device__ __forceinline__ void build_cta_bounds(int* bound, float* wtmp, int to
     }
     if (tid == 0) bound[0] = 0;
   }
-  __syncthreads();
+  bar_sync(1, nthr);
 }
 
 // The CTA whose range holds tile g: largest c with bound[c] <= g.
@@ -495,8 +507,9 @@ struct SmemLayout {
   static constexpr int kBarOff = kScaleOff + kScaleBytes;
   static constexpr int kNumBars = 2 * NSTAGE * kHeadsPerCta + 4 * NSTAGE;
   static constexpr int kAbortOff = kBarOff + kNumBars * 8;
-  static constexpr int kSibOff = kAbortOff + 16;                       // [8] per-head hand-over counters (WPH = 2)
-  static constexpr int kBoundOff = kSibOff + 32;                       // tile range bounds per CTA
+  static constexpr int kSibOff = kAbortOff + 16;                       // [8] per-head hand-over counters (WPH = 2),
+                                                                       // then [8] help flags, [8] lo, [8] hi
+  static constexpr int kBoundOff = kSibOff + 128;                      // tile range bounds per CTA
   static constexpr int kWeightOff = kBoundOff + (kMaxCtas + 1) * 4;    // split weights (floats)
   static constexpr int kPrefixOff = kWeightOff + kMaxCtas * 4;
   static constexpr int kTotal = kPrefixOff + (kMaxBatch + 1) * 4 + 1024;  // +1024: manual alignment
@@ -591,38 +604,19 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
         mbar_init(scale_full(ring, s), 1);
       }
     *abort_flag = 0;
-    for (int h = 0; h < kHeadsPerCta; ++h) reinterpret_cast<volatile int*>(sgen + L::kSibOff)[h] = 0;
+    for (int h = 0; h < 4 * kHeadsPerCta; ++h) reinterpret_cast<volatile int*>(sgen + L::kSibOff)[h] = 0;
     fence_barrier_init();
   }
-  build_tile_prefix(prefix, p.seq_lens, p.batch, p.page_size, p.tiles_per_page, p.force_empty != 0);
   const uint64_t epoch = (p.epoch_base ? *reinterpret_cast<const volatile uint64_t*>(p.epoch_base) : 0ull) +
                          p.epoch_rel;
-
-  const int total = prefix[p.batch];
   int* bound = reinterpret_cast<int*>(sgen + L::kBoundOff);
   float* cta_weight = reinterpret_cast<float*>(sgen + L::kWeightOff);
-  build_cta_bounds(bound, cta_weight, total, p.n_cta_x, p.obs_read);
-  const int g0 = bound[blockIdx.x];
-  const int g1 = bound[blockIdx.x + 1];
-  const unsigned long long t_start = global_ns();
-  // every on-chip wait ends by then: the longest legitimate stall (a peer whose query is
-  // late) plus two seconds
-  const unsigned long long pipe_deadline = t_start + p.q_timeout_ns + 2000000000ull;
-  if (threadIdx.x == 0) trace_first(p, 0);
-  if (p.stats && threadIdx.x == 0 && blockIdx.x == 0) {
-    if (blockIdx.y == 0) atomicAdd(p.stats, 1ull);
-    atomicAdd(p.stats + 1, (unsigned long long)total * (unsigned long long)heads_here);   // (tile, kv-head) units
-  }
-  if (p.obs_write && warp == 0 && lane == 0 && blockIdx.y == 0) {
-    if (blockIdx.x == 0) p.obs_write[0] = (uint32_t)p.n_cta_x;
-    if (g0 >= g1) {                       // nothing to time: keep the weight, no rate
-      p.obs_write[1 + 3 * blockIdx.x] = 0u;
-      p.obs_write[2 + 3 * blockIdx.x] = 0u;
-      p.obs_write[3 + 3 * blockIdx.x] = __float_as_uint(1.f);
-    }
-  }
+  // The service warp (the last one) does not help with the tile list: on the home GPU it
+  // pushes the query out FIRST, while the memory system is still idle, so the peers can
+  // start as early as possible.  The other warps build the list among themselves (barrier
+  // 1) and announce it on barrier 2, where the service warp picks it up.
+  constexpr int kWorkThreads = (kConsumerWarps + kProducerWarps) * 32;
   if (warp == kServiceWarp) {
-    // ---------------------------- service warp ---------------------------- //
     const int n_warps = gridDim.x * gridDim.y, my_warp = blockIdx.y * gridDim.x + blockIdx.x;
     if (p.pub_n > 0) {
       // Home GPU: the service warps of the grid share the (sequence, peer) pairs; each
@@ -659,6 +653,36 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
         if (lane == 0) trace_first(p, 1);
       }
     }
+    bar_sync(2, kWorkThreads + 32);
+  } else {
+    build_tile_prefix(prefix, p.seq_lens, p.batch, p.page_size, p.tiles_per_page, p.force_empty != 0,
+                      kWorkThreads);
+    build_cta_bounds(bound, cta_weight, prefix[p.batch], p.n_cta_x, p.obs_read, kWorkThreads);
+    __threadfence_block();
+    bar_arrive(2, kWorkThreads + 32);
+  }
+  const int total = prefix[p.batch];
+  const int g0 = bound[blockIdx.x];
+  const int g1 = bound[blockIdx.x + 1];
+  const unsigned long long t_start = global_ns();
+  // every on-chip wait ends by then: the longest legitimate stall (a peer whose query is
+  // late) plus two seconds
+  const unsigned long long pipe_deadline = t_start + p.q_timeout_ns + 2000000000ull;
+  if (threadIdx.x == 0) trace_first(p, 0);
+  if (p.stats && threadIdx.x == 0 && blockIdx.x == 0) {
+    if (blockIdx.y == 0) atomicAdd(p.stats, 1ull);
+    atomicAdd(p.stats + 1, (unsigned long long)total * (unsigned long long)heads_here);   // (tile, kv-head) units
+  }
+  if (p.obs_write && warp == 0 && lane == 0 && blockIdx.y == 0) {
+    if (blockIdx.x == 0) p.obs_write[0] = (uint32_t)p.n_cta_x;
+    if (g0 >= g1) {                       // nothing to time: keep the weight, no rate
+      p.obs_write[1 + 3 * blockIdx.x] = 0u;
+      p.obs_write[2 + 3 * blockIdx.x] = 0u;
+      p.obs_write[3 + 3 * blockIdx.x] = __float_as_uint(1.f);
+    }
+  }
+  if (warp == kServiceWarp) {
+    // ---------------------------- service warp ---------------------------- //
     // Sequences with no token in this shard have no CTA of their own.  Their rows
     // (neutral, or -- on the home GPU -- the merge of the peers' rows) are written by the
     // service warps: unit (empty sequence e, kv-head h) goes to the service warp of CTA
@@ -815,9 +839,31 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
 
   const bool ps16 = (p.page_size % kTileTok) == 0;
 
+  // What the last CTA of a (sequence, kv-head) does for q heads qh0 .. qh0+nq-1 once the
+  // pair's slots lo..hi are complete: the final merge and the rows' way out.
+  auto finish_unit = [&](int seq, int qh0, int nq, int lo, int hi) {
+    bool ok = true;
+    if (p.mg_n > 0) {
+      // Home GPU: the peers' rows of this pair are needed, and they usually arrive later
+      // than this.  Fold the pair's own slots into one (unnormalised) slot first, so
+      // that what is left to do once the tags are here is one round of loads.
+      const int us = p.unit_slot0 + seq;
+      combine_group<(WPH > 1)>(p, seq, qh0, nq, lo, hi, lane, us);
+      __threadfence_block();
+      __syncwarp();
+      lo = hi = us;
+      if (lane == 0) trace_max(p, 3);
+      ok = wait_peer_tags(p, epoch, (int64_t)seq * p.n_q_heads + qh0, lane);
+    } else if (lane == 0) {
+      trace_max(p, 3);
+    }
+    if (ok) {
+      combine_group<(WPH > 1)>(p, seq, qh0, nq, lo, hi, lane);
+      release_unit(p, epoch, seq, qh0, nq, lane);
+    }
+  };
+
   int s = find_seq(prefix, p.batch, g0);
-  int it = 0, stage = 0;           // tile counter of this CTA and its ring slot / phase
-  uint32_t ph = 0;
   for (int gt = g0; gt < g1;) {
     while (prefix[s + 1] <= gt) ++s;
     const int seg_end = min(g1, prefix[s + 1]);
@@ -930,9 +976,15 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     const int n_seq_tiles = prefix[s + 1] - prefix[s];
 
-    for (int ti = gt - prefix[s]; gt < seg_end;
-         ++gt, ++ti, ++it, stage = (stage + 1 == NSTAGE ? 0 : stage + 1), ph ^= (stage == 0)) {
+    const int tile_base = prefix[s];
+    for (; gt < seg_end; ++gt) {
+      // tile counter of this CTA, its ring slot and phase, and the tile's index in its sequence:
+      // all derived from gt, so that nothing but gt is carried around the loop
+      const int it = gt - g0;
       if (WPH > 1 && (it & (WPH - 1)) != par) continue;   // the sibling warp's tile
+      const int stage = it % NSTAGE;
+      const uint32_t ph = (uint32_t)(it / NSTAGE) & 1u;
+      const int ti = gt - tile_base;
       // valid tokens of this tile: 16 except on a sequence's last tile (pages that are a
       // multiple of 16 tokens), else from the tile's position inside its page
       int valid = kTileTok;
@@ -974,10 +1026,8 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
               const uint32_t chunk = (kp << 1) | kcsel;
               ldmatrix_x4(r, sk + krow_off + ((chunk ^ kx) << 4));
               mma_16832_e4m3(sa, r, qf[kp][0], qf[kp][1]);
-              mma_16832_e4m3(sb, r, qf[4 + kp][0], qf[4 + kp][1]);
+              mma_16832_e4m3(sa, r, qf[4 + kp][0], qf[4 + kp][1]);
             }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) sa[i] += sb[i];
           }
           // per-token K scales (rows g and g+8 of the score tile)
           got = pipe_wait(scale_full(0, stage), ph, abort_flag, pipe_deadline);
@@ -1186,7 +1236,29 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
           __threadfence();
           __syncwarp();
           if (lane == 0) reinterpret_cast<volatile int*>(sgen + L::kSibOff)[hh] = s + 1;
-          continue;                  // the first warp of the pair takes it from here
+          if (!p.fuse) continue;
+          // The first warp of the pair counts the CTA in.  If that made this CTA the last one
+          // of the (sequence, kv-head), the merge of the pair's slots is shared: the first
+          // warp takes the first half of the group's q heads, this one the second half.
+          volatile int* help = reinterpret_cast<volatile int*>(sgen + L::kSibOff) + kHeadsPerCta + hh;
+          int verdict = 0;
+          if (lane == 0) {
+            for (uint32_t w = 0;; ++w) {
+              const int v = *help;
+              if (v == s + 1 || v == -(s + 1)) { verdict = v; break; }
+              if (*abort_flag) break;
+              if ((w & 63u) == 63u && global_ns() > pipe_deadline) { pipe_failed(p, abort_flag); break; }
+            }
+          }
+          verdict = __shfl_sync(0xffffffffu, verdict, 0);
+          if (verdict == 0) return;
+          __syncwarp();
+          const int first = (G + 1) / 2;
+          if (verdict > 0 && G > first) {
+            const int lo2 = help[kHeadsPerCta], hi2 = help[2 * kHeadsPerCta];
+            finish_unit(s, kvh * G + first, G - first, lo2, hi2);
+          }
+          continue;
         }
       }
     }
@@ -1243,13 +1315,19 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
           hi = p.grp_slot0 + g_hi + s;
         }
       }
-      if (last && lane == 0) trace_max(p, 3);
-      if (last && p.mg_n > 0)    // home: the peers' rows of this pair are needed
-        last = wait_peer_tags(p, epoch, (int64_t)s * p.n_q_heads + (int64_t)kvh * G, lane) ? 1 : 0;
-      if (last) {
-        combine_group<(WPH > 1)>(p, s, kvh * G, G, lo, hi, lane);
-        release_unit(p, epoch, s, kvh * G, G, lane);
+      int mine = G;                       // q heads of the group this warp merges
+      if constexpr (WPH > 1) {
+        // tell the second warp of the pair whether there is a merge to share, and over which slots
+        volatile int* help = reinterpret_cast<volatile int*>(sgen + L::kSibOff) + kHeadsPerCta + hh;
+        if (lane == 0) {
+          help[kHeadsPerCta] = lo;
+          help[2 * kHeadsPerCta] = hi;
+          __threadfence_block();
+          *help = last ? s + 1 : -(s + 1);
+        }
+        mine = (G + 1) / 2;
       }
+      if (last) finish_unit(s, kvh * G, mine, lo, hi);
     }
   }
 }
