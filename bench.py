@@ -719,15 +719,26 @@ def measure_workload(name, args, N, rank, local_rank, dev, steps, headline):
     qdt = wl["q_dtype"]
 
     torch.manual_seed(7)
-    q_host = torch.randn(B, HQ, D).to(qdt).pin_memory()
-    q = q_host.to(dev)
-    out = torch.zeros(B, HQ, D, dtype=qdt, device=dev)
-    out_host = torch.empty(B, HQ, D, dtype=qdt).pin_memory()
-    len_host = my_len.cpu().pin_memory()
+    # One pinned staging buffer per rank holds everything a decode step can change -- the
+    # query (home rank), every sequence's shard length and one page id per sequence -- and
+    # one device buffer mirrors it: q, the lengths and the new page ids are views of it, so
+    # the end-to-end step is ONE host-to-device copy per rank.
+    q_bytes = B * HQ * D * 2
+    stage_host = torch.zeros(q_bytes + 8 * B, dtype=torch.uint8).pin_memory()
+    stage_dev = torch.zeros(q_bytes + 8 * B, dtype=torch.uint8, device=dev)
+    q_host = stage_host[:q_bytes].view(qdt).view(B, HQ, D)
+    q_host.copy_(torch.randn(B, HQ, D).to(qdt))
+    q = stage_dev[:q_bytes].view(qdt).view(B, HQ, D)
+    len_dev = stage_dev[q_bytes:q_bytes + 4 * B].view(torch.int32)
+    new_page_dev = stage_dev[q_bytes + 4 * B:].view(torch.int32)
+    stage_host[q_bytes:q_bytes + 4 * B].view(torch.int32).copy_(my_len.cpu())
     # the page a decode step may have to add per sequence: the last one of each row
     used = ((my_len.to(torch.int64) + PAGE - 1) // PAGE - 1).clamp_(min=0)
-    new_page_host = my_tab.gather(1, used.view(-1, 1)).view(-1).cpu().pin_memory()
-    new_page_dev = torch.empty(B, dtype=torch.int32, device=dev)
+    stage_host[q_bytes + 4 * B:].view(torch.int32).copy_(my_tab.gather(1, used.view(-1, 1)).view(-1).cpu())
+    stage_dev.copy_(stage_host)
+    my_len = len_dev                       # the kernels read the lengths where the copy lands
+    out = torch.zeros(B, HQ, D, dtype=qdt, device=dev)
+    out_host = torch.empty(B, HQ, D, dtype=qdt).pin_memory()
     rows = torch.arange(B, device=dev)
     scale = 1.0 / math.sqrt(D)
     view = ops.paged_view(pool[0], pool[1], *(wl["scales"] or (None, None)))
@@ -814,9 +825,9 @@ def measure_workload(name, args, N, rank, local_rank, dev, steps, headline):
             # what a decode step changes: the query, every sequence's length on the GPU that
             # took the new token, and at most one new page id per sequence
             if rank == 0:
-                q.copy_(q_host, non_blocking=True)
-            my_len.copy_(len_host, non_blocking=True)
-            new_page_dev.copy_(new_page_host, non_blocking=True)
+                stage_dev.copy_(stage_host, non_blocking=True)
+            else:
+                stage_dev[q_bytes:].copy_(stage_host[q_bytes:], non_blocking=True)
             my_tab[rows, used] = new_page_dev
             step()
             if rank == 0:
@@ -826,12 +837,13 @@ def measure_workload(name, args, N, rank, local_rank, dev, steps, headline):
             e2e_step()
         e2e_n = 3 if args.lean else max(5, min(steps, 100))
         e2e_ms = timed(e2e_step, e2e_n) / e2e_n
-        h2d = q_host.numel() * 2 + N * (len_host.numel() * 4 + new_page_host.numel() * 4)
+        h2d = q_bytes + N * 8 * B
         e2e = {"value": algo_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": out_host.numel() * 2,
-               "note": "per step, from pinned host memory: q to GPU 0, and to every GPU its shard lengths "
+               "note": "per step, one copy per GPU from pinned host memory: q (GPU 0 only), the shard lengths "
                        "and one page id per sequence (what a decode step can change; the block tables stay "
-                       "resident); the result is copied back to the host and GPU 0's stream synchronised"}
+                       "resident and take the page ids by a scatter); the result is copied back to the host "
+                       "and GPU 0's stream synchronised"}
 
     # ---- the shard kernel alone on every rank, CUDA events around each launch -------- #
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))

@@ -1148,7 +1148,6 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
       __syncwarp();
       if (lane == 0) mbar_arrive(empty(1, stage));
     }
-
     if (gt >= g1 && p.obs_write && warp == 0 && lane == 0 && blockIdx.y == 0) {
       // this CTA's tiles are done: what the next launch's split is computed from
       const unsigned long long t_end = global_ns();
