@@ -373,6 +373,7 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
     p.mg_tag_stride = (int64_t)x->lse_part_elems;
     p.mg_timeout_ns = kWaitNs;
     p.mg_status = x->status;
+    p.pub_count = reinterpret_cast<unsigned int*>(reinterpret_cast<uint8_t*>(x->status) + 512);
     for (int r = 0; r < x->world; ++r) {
       if (r == x->rank) continue;
       p.pub_q[p.pub_n] = reinterpret_cast<uint4*>(x->peer_slab[r] + x->off_q);
@@ -794,8 +795,9 @@ int pkv_exchange_create(pkv_exchange** out, int device, int rank, int world, int
   x->slab_bytes = x->off_qtags + align_up((size_t)max_batch * sizeof(uint64_t), 256);
   cudaError_t e = cudaMalloc(&x->slab, x->slab_bytes);
   if (e == cudaSuccess) e = cudaMemset(x->slab, 0, x->slab_bytes);
-  if (e == cudaSuccess) e = cudaMalloc(&x->status, 512);
-  if (e == cudaSuccess) e = cudaMemset(x->status, 0, 512);
+  const size_t status_bytes = 512 + sizeof(unsigned int) * (size_t)max_batch * world;   // status, epoch base, publish counters
+  if (e == cudaSuccess) e = cudaMalloc(&x->status, status_bytes);
+  if (e == cudaSuccess) e = cudaMemset(x->status, 0, status_bytes);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
     pkv_exchange_destroy(x);

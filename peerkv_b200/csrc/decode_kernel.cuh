@@ -102,9 +102,10 @@ struct DecodeParams {
   // launch on this shard; written for the next one.  Word 0 is the CTA count they refer to.
   const uint32_t* obs_read;
   uint32_t* obs_write;
-  // home GPU only -- q publish in the prologue: the service warps store q [B][Hq][128] into
-  // every peer's inbox and release that peer's per-sequence q tags.
+  // home GPU only -- q publish in the prologue: all warps store q [B][Hq][128] into every
+  // peer's inbox; the one that completes a (sequence, peer) pair releases its tag.
   int pub_n;
+  unsigned int* pub_count;     // [batch * pub_n] chunk counters, zero between launches
   uint4* pub_q[kMaxWorld];
   uint64_t* pub_tags[kMaxWorld];
   // home GPU only -- final merge in the tail: after a (sequence, kv-head) is combined locally
@@ -611,48 +612,49 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
                          p.epoch_rel;
   int* bound = reinterpret_cast<int*>(sgen + L::kBoundOff);
   float* cta_weight = reinterpret_cast<float*>(sgen + L::kWeightOff);
-  // The service warp (the last one) does not help with the tile list: on the home GPU it
-  // pushes the query out FIRST, while the memory system is still idle, so the peers can
-  // start as early as possible.  The other warps build the list among themselves (barrier
-  // 1) and announce it on barrier 2, where the service warp picks it up.
+  // The service warp (the last one) does not help with the tile list: the other warps build
+  // it among themselves (barrier 1) and announce it on barrier 2, where the service warp
+  // picks it up.
   constexpr int kWorkThreads = (kConsumerWarps + kProducerWarps) * 32;
-  if (warp == kServiceWarp) {
-    const int n_warps = gridDim.x * gridDim.y, my_warp = blockIdx.y * gridDim.x + blockIdx.x;
-    if (p.pub_n > 0) {
-      // Home GPU: the service warps of the grid share the (sequence, peer) pairs; each
-      // stores one sequence's query rows into one peer's inbox.  All stores of a warp go
-      // out first, then one system fence, then the per-sequence tags.
-      const int row16 = p.n_q_heads * (kHeadDim * 2 / 16);        // 16-byte words per sequence
-      const int n_pairs = p.batch * p.pub_n;
-      for (int pair = my_warp; pair < n_pairs; pair += n_warps) {
-        const int b = pair / p.pub_n, j = pair - b * p.pub_n;
-        const uint4* src = reinterpret_cast<const uint4*>(p.q) + (int64_t)b * row16;
-        uint4* dst = p.pub_q[j] + (int64_t)b * row16;
-        for (int i0 = 0; i0 < row16; i0 += 32 * 8) {
-          uint4 v[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int i = i0 + u * 32 + lane;
-            if (i < row16) v[u] = __ldcg(src + i);
-          }
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int i = i0 + u * 32 + lane;
-            if (i < row16) dst[i] = v[u];
+  if (p.pub_n > 0) {
+    // Home GPU: before anything else, and while the memory system is still idle, EVERY warp
+    // of the grid pushes a slice of the query out: a chunk is 512 bytes (one 16-byte word per
+    // lane) of one sequence's rows for one peer.  A warp fences its own stores, then counts
+    // its chunks in; whoever completes a (sequence, peer) pair stores that pair's tag.  This
+    // takes the publish from ~10 us (one warp per 8 KB pair) to the latency of one load, one
+    // store, one system fence and one atomic.
+    const int row16 = p.n_q_heads * (kHeadDim * 2 / 16);          // 16-byte words per sequence
+    const int cpp = (row16 + 31) / 32;                            // chunks per pair
+    const int n_chunks = p.batch * p.pub_n * cpp;
+    const int n_warps_cta = blockDim.x >> 5;
+    const int gw = (blockIdx.y * gridDim.x + blockIdx.x) * n_warps_cta + warp;
+    const int n_gw = gridDim.x * gridDim.y * n_warps_cta;
+    for (int c = gw; c < n_chunks; c += n_gw) {
+      const int pair = c / cpp, word = (c - pair * cpp) * 32 + lane;
+      const int b = pair / p.pub_n, j = pair - b * p.pub_n;
+      if (word < row16)
+        p.pub_q[j][(int64_t)b * row16 + word] = __ldcg(reinterpret_cast<const uint4*>(p.q) + (int64_t)b * row16 + word);
+    }
+    if (gw < n_chunks) {
+      __threadfence_system();
+      __syncwarp();
+      if (lane == 0) {
+        for (int c = gw; c < n_chunks; c += n_gw) {
+          const int pair = c / cpp;
+          const unsigned int prev = atomicAdd(p.pub_count + pair, 1u);
+          if (prev == (unsigned int)(cpp - 1)) {
+            p.pub_count[pair] = 0;                                // ready for the next step
+            __threadfence();
+            const int b = pair / p.pub_n, j = pair - b * p.pub_n;
+            st_release_sys_u64(p.pub_tags[j] + b, epoch);
+            trace_max(p, 1);
           }
         }
       }
-      if (my_warp < n_pairs) {
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0)
-          for (int pair = my_warp; pair < n_pairs; pair += n_warps) {
-            const int b = pair / p.pub_n, j = pair - b * p.pub_n;
-            st_release_sys_u64(p.pub_tags[j] + b, epoch);
-          }
-        if (lane == 0) trace_first(p, 1);
-      }
+      __syncwarp();
     }
+  }
+  if (warp == kServiceWarp) {
     bar_sync(2, kWorkThreads + 32);
   } else {
     build_tile_prefix(prefix, p.seq_lens, p.batch, p.page_size, p.tiles_per_page, p.force_empty != 0,
