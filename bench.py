@@ -757,6 +757,7 @@ def measure_workload(name, args, N, rank, local_rank, dev, steps, headline):
         from peerkv_b200.distributed import DistPeerGroup
         grp = DistPeerGroup(dev, B, HQ, home=0)
         shard = grp.shard
+        _GROUP["grp"] = grp
 
         def step():
             grp.step(a, q=q, out=out)
@@ -904,6 +905,33 @@ def measure_workload(name, args, N, rank, local_rank, dev, steps, headline):
     return res
 
 
+_GROUP = {}
+
+
+def hop_latency(L, shard, dev, N, rank, iters=2000):
+    """One-way latency between GPU 0 and GPU 1 of a bare flag, and of a payload + system
+    fence + flag (what a partial return is), measured by the library's probe kernels."""
+    import torch
+    import torch.distributed as dist
+    from peerkv_b200 import _lib, ops
+    xchg = _GROUP["grp"].xchg
+    out = torch.zeros(2, dtype=torch.int64, device=dev)
+    res = {}
+    for name, payload in (("flag_only", 0), ("payload_4096B_fence_flag", 4096)):
+        if rank < 2:
+            _lib.check(L.pkv_exchange_hop_probe_reset(xchg._h, ops._stream(dev)))
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank < 2:
+            _lib.check(L.pkv_exchange_hop_probe(xchg._h, 1 - rank, rank, iters, payload, out.data_ptr(), ops._stream(dev)))
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == 0:
+            ns, bad = int(out[0]), int(out[1])
+            res[name] = None if bad else ns / (2.0 * iters) / 1e3
+    return res if rank == 0 else None
+
+
 def step_timeline(L, shard, step, barrier, dev, N, rank, reps=5):
     """%globaltimer stamps of one step in steady state (three untraced steps are queued in
     front of the traced one, no host synchronisation in between), per rank, in microseconds
@@ -942,12 +970,14 @@ def step_timeline(L, shard, step, barrier, dev, N, rank, reps=5):
         dist.all_gather_object(allr, mine)
     else:
         allr = [mine]
+    hops = hop_latency(L, shard, dev, N, rank) if N > 1 else None
     if rank != 0:
         return None
     base = allr[0]["first_cta_start_ns"]
     for r in allr:      # the GPUs' timers are separate clocks: only a rough cross-rank offset
         r["first_cta_start_vs_rank0_us"] = (r.pop("first_cta_start_ns") - base) / 1e3
-    return {"unit": "us after the rank's first CTA start; rank 0 is the home GPU", "ranks": allr}
+    return {"unit": "us after the rank's first CTA start; rank 0 is the home GPU", "ranks": allr,
+            "fabric_one_way_us": hops}
 
 
 def main():

@@ -323,6 +323,19 @@ int pkv_exchange_capture_begin(pkv_exchange* x);
 int pkv_exchange_capture_end(pkv_exchange* x, void* stream, uint64_t* steps_out);
 int pkv_exchange_replayed(pkv_exchange* x);
 
+/* Measurement aid: what a hop over the fabric costs, with the primitives the decode kernels
+ * use.  Rank A calls it with role 0 and rank B with role 1 (peer_rank = the other one), at
+ * about the same time, after both called pkv_exchange_hop_probe_reset and synchronised.
+ * The two single-warp kernels bounce a flag `iters` times; with payload_bytes > 0 (a
+ * multiple of 512) every bounce first stores that many bytes into the other GPU's q inbox
+ * and passes a system fence, as a partial return does.  out (2 x uint64 of device memory on
+ * this rank's GPU): elapsed ns of this side; 1 if a wait ran out (bounded, 2 s).  One-way
+ * latency = out[0] of role 0 / (2 * iters).  Not to be mixed with steps in flight (the
+ * inbox is overwritten).  No counterpart in the reference. */
+int pkv_exchange_hop_probe(pkv_exchange* x, int32_t peer_rank, int32_t role, int32_t iters,
+                           int32_t payload_bytes, uint64_t* out, void* stream);
+int pkv_exchange_hop_probe_reset(pkv_exchange* x, void* stream);
+
 /* Home rank, start of a step in the three-call form (publish, partial, merge): advances
  * the epoch, stores q ([batch, n_q_heads, 128], 16-bit) into every attached peer's q
  * inbox with P2P stores and releases the per-sequence tags.  Replaces the q broadcast +

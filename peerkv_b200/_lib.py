@@ -24,6 +24,7 @@ EXPORTS = [
     "pkv_exchange_capture_end", "pkv_exchange_replayed",
     "pkv_add_rmsnorm", "pkv_rope_append", "pkv_swiglu", "pkv_kv_append",
     "pkv_enable_peer_access", "pkv_shard_stats", "pkv_prefill_partial", "pkv_stage_peer_blocks",
+    "pkv_exchange_hop_probe", "pkv_exchange_hop_probe_reset",
 ]
 
 
@@ -102,6 +103,8 @@ def lib():
         "pkv_shard_stats": [vp, vp, P(u64), P(u64)],
         "pkv_stage_peer_blocks": [C.c_int, vp, i64, vp, i32, i32, i32, P(i64), P(i64), P(vp), P(vp), P(i64), vp, vp,
                                   i64, i64, i64, i64, i32, vp, vp, vp, vp],
+        "pkv_exchange_hop_probe": [vp, i32, i32, i32, i32, vp, vp],
+        "pkv_exchange_hop_probe_reset": [vp, vp],
         "pkv_prefill_partial": [C.c_int, vp, i64, i64, i64, vp, vp, i64, i64, i64, i32, i32, i32, i32, i32, i32, i32,
                                 f32, i32, i64, i64, vp, vp, vp],
         "pkv_kv_append": [C.c_int, vp, vp, i64, vp, i32, i32, i32, i32, i32, P(i64), P(i64), P(vp), P(vp),

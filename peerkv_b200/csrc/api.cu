@@ -124,7 +124,7 @@ struct pkv_exchange {
   uint64_t base_host = 0;                   // host mirror of the device-resident epoch base
   uint64_t cap_epoch0 = 0, cap_steps = 0;   // graph capture: epoch at its start, steps it holds
   bool capturing = false;
-  size_t off_q = 0, off_qtags = 0, off_o = 0, off_lse = 0, off_tags = 0, slab_bytes = 0;
+  size_t off_q = 0, off_qtags = 0, off_o = 0, off_lse = 0, off_tags = 0, off_probe = 0, slab_bytes = 0;
   size_t o_part_elems = 0, lse_part_elems = 0;
 };
 
@@ -792,7 +792,8 @@ int pkv_exchange_create(pkv_exchange** out, int device, int rank, int world, int
   x->off_lse = x->off_o + align_up(world * x->o_part_elems * sizeof(float), 256);
   x->off_tags = x->off_lse + align_up(world * x->lse_part_elems * sizeof(float), 256);
   x->off_qtags = x->off_tags + align_up(world * x->lse_part_elems * sizeof(uint64_t), 256);
-  x->slab_bytes = x->off_qtags + align_up((size_t)max_batch * sizeof(uint64_t), 256);
+  x->off_probe = x->off_qtags + align_up((size_t)max_batch * sizeof(uint64_t), 256);   // one flag for pkv_exchange_hop_probe
+  x->slab_bytes = x->off_probe + 256;
   cudaError_t e = cudaMalloc(&x->slab, x->slab_bytes);
   if (e == cudaSuccess) e = cudaMemset(x->slab, 0, x->slab_bytes);
   const size_t status_bytes = 512 + sizeof(unsigned int) * (size_t)max_batch * world;   // status, epoch base, publish counters
@@ -1043,6 +1044,34 @@ int pkv_home_merge(pkv_exchange* x, int32_t batch, uint32_t wait_mask, void* out
   Range range("pkv:home_merge(wait+merge)");
   pkv::merge_partials_kernel<<<(m.rows + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(m);
   PKV_CUDA(cudaGetLastError());
+  return PKV_OK;
+}
+
+int pkv_exchange_hop_probe(pkv_exchange* x, int32_t peer_rank, int32_t role, int32_t iters, int32_t payload_bytes,
+                           uint64_t* out, void* stream) {
+  if (!x || !out) return fail(PKV_E_INVALID, "null pointer");
+  if (peer_rank < 0 || peer_rank >= x->world || peer_rank == x->rank || !x->peer_slab[peer_rank])
+    return fail(PKV_E_STATE, "rank %d is not an attached peer", peer_rank);
+  if ((role != 0 && role != 1) || iters <= 0 || iters > 1000000) return fail(PKV_E_INVALID, "role %d iters %d", role, iters);
+  const size_t inbox = (size_t)x->max_batch * x->n_q_heads * pkv::kHeadDim * 2;
+  if (payload_bytes < 0 || payload_bytes % 512 || (size_t)payload_bytes > inbox)
+    return fail(PKV_E_INVALID, "payload_bytes %d: a multiple of 512, at most the q inbox (%zu)", payload_bytes, inbox);
+  DeviceGuard guard(x->device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", x->device);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  pkv::hop_probe_kernel<<<1, 32, 0, st>>>(
+      role, iters, payload_bytes / 512, reinterpret_cast<uint4*>(x->peer_slab[peer_rank] + x->off_q),
+      reinterpret_cast<uint64_t*>(x->peer_slab[peer_rank] + x->off_probe),
+      reinterpret_cast<const uint64_t*>(x->slab + x->off_probe), kWaitNs, reinterpret_cast<unsigned long long*>(out));
+  PKV_CUDA(cudaGetLastError());
+  return PKV_OK;
+}
+
+int pkv_exchange_hop_probe_reset(pkv_exchange* x, void* stream) {
+  if (!x) return fail(PKV_E_INVALID, "null exchange");
+  DeviceGuard guard(x->device);
+  if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", x->device);
+  PKV_CUDA(cudaMemsetAsync(x->slab + x->off_probe, 0, 256, static_cast<cudaStream_t>(stream)));
   return PKV_OK;
 }
 

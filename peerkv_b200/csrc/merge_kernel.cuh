@@ -42,6 +42,47 @@ __global__ void __launch_bounds__(1024) publish_q_kernel(const PublishParams p) 
   for (int b = threadIdx.x; b < p.batch; b += blockDim.x) st_release_sys_u64(p.tags[blockIdx.x] + b, epoch);
 }
 
+// Measurement aid: round-trip time of the two things a step sends over the fabric, with
+// the primitives the decode kernels use.  Two single-warp kernels on two GPUs bounce a flag
+// `iters` times; with payload_words > 0 each bounce first stores that many 512-byte lines
+// into the other GPU's inbox and passes a system fence, as a partial return does.  role 0
+// starts, role 1 answers; out[0] = elapsed ns of this side, out[1] = 1 if a wait ran out
+// (every wait is bounded by `timeout_ns`).
+__global__ void __launch_bounds__(32) hop_probe_kernel(int role, int iters, int payload_words, uint4* remote_buf,
+                                                       uint64_t* remote_flag, const uint64_t* my_flag,
+                                                       unsigned long long timeout_ns, unsigned long long* out) {
+  const int lane = threadIdx.x;
+  unsigned long long t0, bad = 0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  auto wait_for = [&](uint64_t v) {
+    if (lane == 0) {
+      unsigned long long s, n;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(s));
+      while (ld_acquire_sys_u64(my_flag) < v) {
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(n));
+        if (n - s > timeout_ns) { bad = 1; break; }
+      }
+    }
+    bad = __shfl_sync(0xffffffffu, bad, 0);
+  };
+  for (int i = 1; i <= iters && !bad; ++i) {
+    if (role == 1) { wait_for((uint64_t)i); if (bad) break; }
+    if (payload_words > 0) {
+      for (int w = 0; w < payload_words; ++w) remote_buf[w * 32 + lane] = make_uint4(i, w, lane, 1u);
+      __threadfence_system();
+      __syncwarp();
+    }
+    if (lane == 0) st_release_sys_u64(remote_flag, (uint64_t)i);
+    if (role == 0) wait_for((uint64_t)i);
+  }
+  if (lane == 0) {
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    out[0] = t1 - t0;
+    out[1] = bad;
+  }
+}
+
 // Adds `step` to a device-resident epoch base: the last node of a captured decode step.
 __global__ void bump_epoch_kernel(uint64_t* base, uint64_t step) { *base += step; }
 
