@@ -909,21 +909,24 @@ _GROUP = {}
 
 
 def hop_latency(L, shard, dev, N, rank, iters=2000):
-    """One-way latency between GPU 0 and GPU 1 of a bare flag, and of a payload + system
-    fence + flag (what a partial return is), measured by the library's probe kernels."""
+    """One-way latency between GPU 0 and GPU 1 of a bare flag, of a payload + system fence +
+    flag (what a partial return is) and of a payload of {payload, epoch} words with nothing
+    behind it (what the query publish is), measured by the library's probe kernels."""
     import torch
     import torch.distributed as dist
     from peerkv_b200 import _lib, ops
     xchg = _GROUP["grp"].xchg
     out = torch.zeros(2, dtype=torch.int64, device=dev)
     res = {}
-    for name, payload in (("flag_only", 0), ("payload_4096B_fence_flag", 4096)):
+    for name, payload, ll in (("flag_only", 0, 0), ("payload_4096B_fence_flag", 4096, 0),
+                              ("payload_4096B_self_validating_words", 4096, 2)):
         if rank < 2:
             _lib.check(L.pkv_exchange_hop_probe_reset(xchg._h, ops._stream(dev)))
         torch.cuda.synchronize()
         dist.barrier()
         if rank < 2:
-            _lib.check(L.pkv_exchange_hop_probe(xchg._h, 1 - rank, rank, iters, payload, out.data_ptr(), ops._stream(dev)))
+            _lib.check(L.pkv_exchange_hop_probe(xchg._h, 1 - rank, rank | ll, iters, payload, out.data_ptr(),
+                                                ops._stream(dev)))
         torch.cuda.synchronize()
         dist.barrier()
         if rank == 0:

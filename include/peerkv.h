@@ -273,16 +273,19 @@ int pkv_kv_append(int device, const void* key, const void* value, int64_t kv_tok
 
 /* ---- several GPUs ------------------------------------------------------- */
 
-/* Mailboxes of one GPU, allocated once: a q inbox with one epoch tag per sequence, and
+/* Mailboxes of one GPU, allocated once: a q inbox of 8-byte {payload, epoch} words, and
  * `world` partial slots ([max_batch, n_q_heads, 128] fp32 O + [max_batch, n_q_heads]
  * lse each) with one epoch tag per (sequence, q head).  rank 0..world-1; the home rank
  * is the one that owns q and runs the merge.  Replaces the per-call stream/event/scratch
  * set-up of csrc/peer_fused_attn_ext.cu:81-97 and its cudaMemcpyAsync hops
  * (:100-101,120-123).
  *
- * Protocol.  Epochs count steps and only grow.  The home GPU stores the query rows of a
- * sequence into each peer's inbox and then that sequence's tag = epoch; a peer reads the
- * rows, and writes anything into the home GPU's slot, only after it has seen the tag.
+ * Protocol.  Epochs count steps and only grow.  The home GPU stores the query rows into
+ * each peer's inbox as 8-byte words, 4 bytes of q and the low 32 bits of the epoch: an
+ * aligned 8-byte store arrives whole, so a word that shows this step's epoch holds this
+ * step's q, and neither a fence nor a flag follows.  A peer re-reads (bounded) the words
+ * it needs until they show the epoch, and writes anything into the home GPU's slot only
+ * after it has seen the first word of that sequence.
  * A peer stores the (O, lse) rows of a (sequence, kv-head) into its slot on the home GPU
  * and then the tags of that group's q heads; the home GPU merges a pair as soon as every
  * awaited rank's tag for it has arrived.  The home GPU publishes epoch e+1 only after its
@@ -328,7 +331,9 @@ int pkv_exchange_replayed(pkv_exchange* x);
  * about the same time, after both called pkv_exchange_hop_probe_reset and synchronised.
  * The two single-warp kernels bounce a flag `iters` times; with payload_bytes > 0 (a
  * multiple of 512) every bounce first stores that many bytes into the other GPU's q inbox
- * and passes a system fence, as a partial return does.  out (2 x uint64 of device memory on
+ * and passes a system fence, as a partial return does.  Roles 2 and 3 are 0 and 1 with the
+ * bounce done the way the query publish does it: the payload as {payload, marker} words,
+ * no fence, no flag, the receiver polling the last 512 bytes.  out (2 x uint64 of device memory on
  * this rank's GPU): elapsed ns of this side; 1 if a wait ran out (bounded, 2 s).  One-way
  * latency = out[0] of role 0 / (2 * iters).  Not to be mixed with steps in flight (the
  * inbox is overwritten).  No counterpart in the reference. */
@@ -338,7 +343,7 @@ int pkv_exchange_hop_probe_reset(pkv_exchange* x, void* stream);
 
 /* Home rank, start of a step in the three-call form (publish, partial, merge): advances
  * the epoch, stores q ([batch, n_q_heads, 128], 16-bit) into every attached peer's q
- * inbox with P2P stores and releases the per-sequence tags.  Replaces the q broadcast +
+ * inbox with P2P stores ({payload, epoch} words).  Replaces the q broadcast +
  * event fork of peer_fused_attn_ext.cu:100-102,114.  pkv_home_step does all three in
  * one launch and is the form to use. */
 int pkv_home_publish_q(pkv_exchange* x, const void* q, int32_t batch, void* stream);
@@ -350,8 +355,8 @@ int pkv_home_publish_q(pkv_exchange* x, const void* q, int32_t batch, void* stre
  * GPU's previous merge itself. */
 int pkv_peer_step(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, int32_t home_rank,
                   int32_t q_override, void* stream);
-/* Home rank, one whole step in ONE launch: the kernel's service warps store q into the
- * peers' inboxes while its other warps already stream the home shard; it combines its
+/* Home rank, one whole step in ONE launch: the kernel first stores q into the peers'
+ * inboxes, all warps sharing the rows, then streams the home shard; it combines its
  * splits and, pair by pair, waits (bounded, device side) for the tags of the ranks in
  * wait_mask and folds their partials in.  out [batch, n_q_heads, 128] in out_dtype;
  * lse_out may be NULL.  An empty home pool (n_pages 0) is fine.  Same result as

@@ -124,7 +124,7 @@ struct pkv_exchange {
   uint64_t base_host = 0;                   // host mirror of the device-resident epoch base
   uint64_t cap_epoch0 = 0, cap_steps = 0;   // graph capture: epoch at its start, steps it holds
   bool capturing = false;
-  size_t off_q = 0, off_qtags = 0, off_o = 0, off_lse = 0, off_tags = 0, off_probe = 0, slab_bytes = 0;
+  size_t off_q = 0, off_o = 0, off_lse = 0, off_tags = 0, off_probe = 0, slab_bytes = 0;
   size_t o_part_elems = 0, lse_part_elems = 0;
 };
 
@@ -142,8 +142,9 @@ float* slot_lse(pkv_exchange* x, int owner_rank, int slot) {
 uint64_t* slot_tags(pkv_exchange* x, int owner_rank, int slot) {
   return reinterpret_cast<uint64_t*>(x->peer_slab[owner_rank] + x->off_tags) + (size_t)slot * x->lse_part_elems;
 }
-uint64_t* q_tags(pkv_exchange* x, int owner_rank) {               // [max_batch]
-  return reinterpret_cast<uint64_t*>(x->peer_slab[owner_rank] + x->off_qtags);
+// query inbox of rank `owner_rank`: [max_batch][n_q_heads][64] 8-byte {payload, epoch} words
+unsigned long long* q_inbox(pkv_exchange* x, int owner_rank) {
+  return reinterpret_cast<unsigned long long*>(x->peer_slab[owner_rank] + x->off_q);
 }
 uint64_t* epoch_base_dev(pkv_exchange* x) {
   return reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(x->status) + 128);
@@ -268,7 +269,7 @@ struct LaunchOut {
   float* o_part = nullptr;
   float* lse_part = nullptr;
   uint64_t* part_tags = nullptr;      // released per (sequence, kv-head) after its rows
-  const uint64_t* q_tags = nullptr;   // peer: wait for the query rows of this epoch
+  const unsigned long long* q_ll = nullptr;   // peer: the query inbox ({payload, epoch} words)
   const uint64_t* epoch_base = nullptr;
   uint64_t epoch_rel = 0;
   bool skip_combine = false;
@@ -335,7 +336,7 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   p.part_o = s->part_o;
   p.part_ml = s->part_ml;
   p.status = s->status;
-  p.q_tags = lo.q_tags;
+  p.q_ll = lo.q_ll;
   p.epoch_base = lo.epoch_base;
   p.epoch_rel = lo.epoch_rel;
   p.q_timeout_ns = kWaitNs;
@@ -373,16 +374,13 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
     p.mg_tag_stride = (int64_t)x->lse_part_elems;
     p.mg_timeout_ns = kWaitNs;
     p.mg_status = x->status;
-    p.pub_count = reinterpret_cast<unsigned int*>(reinterpret_cast<uint8_t*>(x->status) + 512);
     for (int r = 0; r < x->world; ++r) {
       if (r == x->rank) continue;
-      p.pub_q[p.pub_n] = reinterpret_cast<uint4*>(x->peer_slab[r] + x->off_q);
-      p.pub_tags[p.pub_n] = q_tags(x, r);
-      ++p.pub_n;
+      p.pub_ll[p.pub_n++] = q_inbox(x, r);
     }
   }
 
-  Range range(lo.home ? "pkv:home_step(publish+partial+merge)" : lo.q_tags ? "pkv:peer_step(partial)" : "pkv:decode");
+  Range range(lo.home ? "pkv:home_step(publish+partial+merge)" : lo.q_ll ? "pkv:peer_step(partial)" : "pkv:decode");
   // An empty pool goes through the same kernel: every sequence counts as empty, no tile is
   // ever loaded (the zeroed tensor maps are not touched), and the service warps write the
   // neutral rows (O = 0, lse = -inf) or, on the home GPU, the merge of the peers' rows.
@@ -788,15 +786,14 @@ int pkv_exchange_create(pkv_exchange** out, int device, int rank, int world, int
   x->o_part_elems = (size_t)max_batch * n_q_heads * pkv::kHeadDim;
   x->lse_part_elems = align_up((size_t)max_batch * n_q_heads, 64);
   x->off_q = 0;
-  x->off_o = align_up((size_t)max_batch * n_q_heads * pkv::kHeadDim * 2, 256);
+  x->off_o = align_up((size_t)max_batch * n_q_heads * (pkv::kHeadDim / 2) * 8, 256);   // 4 payload bytes per 8-byte word
   x->off_lse = x->off_o + align_up(world * x->o_part_elems * sizeof(float), 256);
   x->off_tags = x->off_lse + align_up(world * x->lse_part_elems * sizeof(float), 256);
-  x->off_qtags = x->off_tags + align_up(world * x->lse_part_elems * sizeof(uint64_t), 256);
-  x->off_probe = x->off_qtags + align_up((size_t)max_batch * sizeof(uint64_t), 256);   // one flag for pkv_exchange_hop_probe
+  x->off_probe = x->off_tags + align_up(world * x->lse_part_elems * sizeof(uint64_t), 256);   // one flag for pkv_exchange_hop_probe
   x->slab_bytes = x->off_probe + 256;
   cudaError_t e = cudaMalloc(&x->slab, x->slab_bytes);
   if (e == cudaSuccess) e = cudaMemset(x->slab, 0, x->slab_bytes);
-  const size_t status_bytes = 512 + sizeof(unsigned int) * (size_t)max_batch * world;   // status, epoch base, publish counters
+  const size_t status_bytes = 512;   // status word, epoch base at byte 128
   if (e == cudaSuccess) e = cudaMalloc(&x->status, status_bytes);
   if (e == cudaSuccess) e = cudaMemset(x->status, 0, status_bytes);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
@@ -943,9 +940,7 @@ int pkv_home_publish_q(pkv_exchange* x, const void* q, int32_t batch, void* stre
   for (int r = 0; r < x->world; ++r) {
     if (r == x->rank) continue;
     if (!x->peer_slab[r]) return fail(PKV_E_STATE, "rank %d is not attached", r);
-    p.dst[n] = reinterpret_cast<uint4*>(x->peer_slab[r] + x->off_q);
-    p.tags[n] = q_tags(x, r);
-    ++n;
+    p.dst[n++] = q_inbox(x, r);
   }
   if (n > 0) {
     DeviceGuard guard(x->device);
@@ -971,8 +966,8 @@ int pkv_peer_step(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, int32
   lo.epoch_base = epoch_base_dev(x);
   lo.epoch_rel = x->epoch + 1 - x->base_host;
   if (!q_override) {
-    aa.q = x->slab + x->off_q;
-    lo.q_tags = q_tags(x, x->rank);
+    aa.q = x->slab + x->off_q;           // not read: the kernel takes the rows from the inbox words
+    lo.q_ll = q_inbox(x, x->rank);
   }
   lo.o_part = slot_o(x, home_rank, x->rank);
   lo.lse_part = slot_lse(x, home_rank, x->rank);
@@ -1052,15 +1047,19 @@ int pkv_exchange_hop_probe(pkv_exchange* x, int32_t peer_rank, int32_t role, int
   if (!x || !out) return fail(PKV_E_INVALID, "null pointer");
   if (peer_rank < 0 || peer_rank >= x->world || peer_rank == x->rank || !x->peer_slab[peer_rank])
     return fail(PKV_E_STATE, "rank %d is not an attached peer", peer_rank);
-  if ((role != 0 && role != 1) || iters <= 0 || iters > 1000000) return fail(PKV_E_INVALID, "role %d iters %d", role, iters);
-  const size_t inbox = (size_t)x->max_batch * x->n_q_heads * pkv::kHeadDim * 2;
-  if (payload_bytes < 0 || payload_bytes % 512 || (size_t)payload_bytes > inbox)
-    return fail(PKV_E_INVALID, "payload_bytes %d: a multiple of 512, at most the q inbox (%zu)", payload_bytes, inbox);
+  if (role < 0 || role > 3 || iters <= 0 || iters > 1000000) return fail(PKV_E_INVALID, "role %d iters %d", role, iters);
+  const int ll = role >> 1;
+  role &= 1;
+  const size_t inbox = (size_t)x->max_batch * x->n_q_heads * pkv::kHeadDim * 4;
+  if (payload_bytes < 0 || payload_bytes % 512 || (size_t)payload_bytes > inbox || (ll && payload_bytes == 0))
+    return fail(PKV_E_INVALID, "payload_bytes %d: a multiple of 512, at most the q inbox (%zu), not 0 with roles 2/3",
+                payload_bytes, inbox);
   DeviceGuard guard(x->device);
   if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", x->device);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   pkv::hop_probe_kernel<<<1, 32, 0, st>>>(
-      role, iters, payload_bytes / 512, reinterpret_cast<uint4*>(x->peer_slab[peer_rank] + x->off_q),
+      role, ll, iters, payload_bytes / 512, reinterpret_cast<uint4*>(x->peer_slab[peer_rank] + x->off_q),
+      reinterpret_cast<const uint4*>(x->slab + x->off_q),
       reinterpret_cast<uint64_t*>(x->peer_slab[peer_rank] + x->off_probe),
       reinterpret_cast<const uint64_t*>(x->slab + x->off_probe), kWaitNs, reinterpret_cast<unsigned long long*>(out));
   PKV_CUDA(cudaGetLastError());

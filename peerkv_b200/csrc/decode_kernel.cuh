@@ -80,9 +80,11 @@ struct DecodeParams {
   // Epochs are `*epoch_base + <relative value>`: the base is a device word that a captured
   // graph bumps once per replay, so the same launch parameters stay valid.  Null = 0.
   const uint64_t* epoch_base;
-  // peer rank: sequence s may be read from q, and its rows written to the home GPU, once
-  // q_tags[s] >= epoch (the home GPU stores the tag after the rows of q).  Null: q is local.
-  const uint64_t* q_tags;
+  // peer rank: the query arrives in this inbox as 8-byte {payload, epoch} words, [B][Hq][64]
+  // (a 16-bit pair per word); a word whose upper half is the step's epoch is this step's.
+  // The first word of a sequence also tells that the home GPU has finished reading the rows
+  // of the previous step, so this rank's slot there may be overwritten.  Null: q is local.
+  const unsigned long long* q_ll;
   uint64_t epoch_rel;
   uint64_t q_timeout_ns;
   // fused combine: the last CTA to finish a sequence merges that sequence's slots
@@ -103,11 +105,9 @@ struct DecodeParams {
   const uint32_t* obs_read;
   uint32_t* obs_write;
   // home GPU only -- q publish in the prologue: all warps store q [B][Hq][128] into every
-  // peer's inbox; the one that completes a (sequence, peer) pair releases its tag.
+  // peer's inbox as {payload, epoch} words; nothing else announces it.
   int pub_n;
-  unsigned int* pub_count;     // [batch * pub_n] chunk counters, zero between launches
-  uint4* pub_q[kMaxWorld];
-  uint64_t* pub_tags[kMaxWorld];
+  unsigned long long* pub_ll[kMaxWorld];
   // home GPU only -- final merge in the tail: after a (sequence, kv-head) is combined locally
   // the same warp waits (bounded) for the peers' tags of that pair and folds their rows in.
   int mg_n;                    // partial slots (ranks); 0 = no merge
@@ -122,7 +122,7 @@ struct DecodeParams {
   // cumulative counters of the shard: [0] launches, [1] (16-token tile, kv-head) units read; or null
   unsigned long long* stats;
   // measurement aid: [CTAs][kTraceWords] %globaltimer stamps, or null
-  //   0 CTA start   1 q published (home) / first q tag seen (peer)   2 last tile consumed
+  //   0 CTA start   1 q published (home) / first q rows seen (peer)   2 last tile consumed
   //   3 last local combine done   4 last peer tag seen (home)   5 last row written
   unsigned long long* trace;
 };
@@ -351,30 +351,38 @@ __device__ __forceinline__ bool wait_peer_tags(const DecodeParams& p, uint64_t e
   return ok;
 }
 
-// Bounded wait of one warp for the query rows of sequence s (peer ranks).  The home GPU
-// stores the tag after the rows, so the rows may be read once this returns true -- and,
-// because the home GPU publishes epoch e only after its merge of epoch e-1 has ended,
-// this rank's slot on the home GPU may be overwritten from then on as well.
-__device__ __forceinline__ bool wait_q_tag(const DecodeParams& p, uint64_t epoch, int s, int lane,
-                                           volatile int* abort_flag) {
-  int ok = 1;
+// A warp's poll of the query inbox found words of an older step: lane 0 decides whether to
+// keep polling (true) or to give up -- the CTA aborted elsewhere, or the query is overdue.
+__device__ __forceinline__ bool q_keep_waiting(const DecodeParams& p, unsigned long long t0, int lane,
+                                               volatile int* abort_flag) {
+  int go = 1;
   if (lane == 0) {
-    ok = 0;
-    const unsigned long long t0 = global_ns();
-    for (;;) {
-      if (ld_acquire_sys_u64(p.q_tags + s) >= epoch) { ok = 1; break; }
-      if (*abort_flag) break;                       // the CTA gave up elsewhere: just leave
-      if (global_ns() - t0 > p.q_timeout_ns) {
-        atomicOr(p.status, kStQTimeout);
-        *abort_flag = 1;
-        break;
-      }
-      __nanosleep(64);
+    if (*abort_flag) {
+      go = 0;                                         // the CTA gave up elsewhere: just leave
+    } else if (global_ns() - t0 > p.q_timeout_ns) {
+      atomicOr(p.status, kStQTimeout);
+      *abort_flag = 1;
+      go = 0;
     }
   }
-  ok = __shfl_sync(0xffffffffu, ok, 0);
-  __syncwarp();
-  return ok != 0;
+  go = __shfl_sync(0xffffffffu, go, 0);
+  if (go) __nanosleep(64);
+  return go != 0;
+}
+
+// Bounded wait of one warp for the first query word of sequence s (peer ranks).  The home
+// GPU publishes the query of step e only after its merge of step e-1 has ended, so from
+// here on this rank's slot on the home GPU may be overwritten.
+__device__ __forceinline__ bool wait_q_first_word(const DecodeParams& p, uint64_t epoch, int s, int lane,
+                                                  volatile int* abort_flag) {
+  const unsigned long long* w = p.q_ll + (int64_t)s * p.n_q_heads * (kHeadDim / 2);
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+    int ok = 1;
+    if (lane == 0) ok = (uint32_t)(ld_ll(w) >> 32) == (uint32_t)epoch;
+    if (__shfl_sync(0xffffffffu, ok, 0)) return true;
+    if (!q_keep_waiting(p, t0, lane, abort_flag)) return false;
+  }
 }
 
 // After a warp has written the rows of (sequence b, q heads qh0 .. qh0+nq-1): make them
@@ -618,13 +626,11 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
   constexpr int kWorkThreads = (kConsumerWarps + kProducerWarps) * 32;
   if (p.pub_n > 0) {
     // Home GPU: before anything else, and while the memory system is still idle, EVERY warp
-    // of the grid pushes a slice of the query out: a chunk is 512 bytes (one 16-byte word per
-    // lane) of one sequence's rows for one peer.  A warp fences its own stores, then counts
-    // its chunks in; whoever completes a (sequence, peer) pair stores that pair's tag.  This
-    // takes the publish from ~10 us (one warp per 8 KB pair) to the latency of one load, one
-    // store, one system fence and one atomic.
+    // of the grid pushes a slice of the query out: a chunk is 512 bytes of q (one 16-byte word
+    // per lane) of one sequence for one peer, stored as 1 KiB of {payload, epoch} words.  No
+    // fence, no counter, no flag: each 8-byte word proves itself to its reader.
     const int row16 = p.n_q_heads * (kHeadDim * 2 / 16);          // 16-byte words per sequence
-    const int cpp = (row16 + 31) / 32;                            // chunks per pair
+    const int cpp = (row16 + 31) / 32;                            // chunks per (sequence, peer)
     const int n_chunks = p.batch * p.pub_n * cpp;
     const int n_warps_cta = blockDim.x >> 5;
     const int gw = (blockIdx.y * gridDim.x + blockIdx.x) * n_warps_cta + warp;
@@ -632,27 +638,12 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
     for (int c = gw; c < n_chunks; c += n_gw) {
       const int pair = c / cpp, word = (c - pair * cpp) * 32 + lane;
       const int b = pair / p.pub_n, j = pair - b * p.pub_n;
-      if (word < row16)
-        p.pub_q[j][(int64_t)b * row16 + word] = __ldcg(reinterpret_cast<const uint4*>(p.q) + (int64_t)b * row16 + word);
-    }
-    if (gw < n_chunks) {
-      __threadfence_system();
-      __syncwarp();
-      if (lane == 0) {
-        for (int c = gw; c < n_chunks; c += n_gw) {
-          const int pair = c / cpp;
-          const unsigned int prev = atomicAdd(p.pub_count + pair, 1u);
-          if (prev == (unsigned int)(cpp - 1)) {
-            p.pub_count[pair] = 0;                                // ready for the next step
-            __threadfence();
-            const int b = pair / p.pub_n, j = pair - b * p.pub_n;
-            st_release_sys_u64(p.pub_tags[j] + b, epoch);
-            trace_max(p, 1);
-          }
-        }
+      if (word < row16) {
+        const int64_t i = (int64_t)b * row16 + word;
+        st_ll_q16(p.pub_ll[j] + 4 * i, __ldcg(reinterpret_cast<const uint4*>(p.q) + i), (uint32_t)epoch);
       }
-      __syncwarp();
     }
+    if (lane == 0 && gw < n_chunks) trace_max(p, 1);
   }
   if (warp == kServiceWarp) {
     bar_sync(2, kWorkThreads + 32);
@@ -699,7 +690,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
           const int qh0 = (head0 + h) * p.group;
           // a peer's rows land in the home GPU's slot: not before the query of this epoch is
           // here, which is also when the home GPU has finished reading the previous rows
-          if (p.q_tags && !wait_q_tag(p, epoch, b, lane, abort_flag)) return;
+          if (p.q_ll && !wait_q_first_word(p, epoch, b, lane, abort_flag)) return;
           bool ok = true;
           if (p.mg_n > 0) ok = wait_peer_tags(p, epoch, (int64_t)b * p.n_q_heads + qh0, lane);
           if (ok) {
@@ -871,11 +862,10 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
     const int seg_end = min(g1, prefix[s + 1]);
     const int len = p.seq_lens[s];
 
-    // The query rows of this epoch are pushed by the home GPU, sequence by sequence.
-    if (p.q_tags) {
-      if (!wait_q_tag(p, epoch, s, lane, abort_flag)) return;
-      if (warp == 0 && lane == 0) trace_first(p, 1);
-    }
+    // On a peer the query rows of this step are pushed by the home GPU as {payload, epoch}
+    // words: the loads below are repeated (bounded) until every word carries this epoch.
+    const int64_t q_row = (int64_t)s * p.n_q_heads + (int64_t)kvh * G + g;
+    const unsigned long long* q_ll_row = p.q_ll ? p.q_ll + q_row * (kHeadDim / 2) : nullptr;
 
     // Q^T B-fragments: column n = g is q head kvh*G + g (zero beyond the group).
     // 16-bit pools: k-step ks covers d = 16ks..16ks+15 in the natural order.
@@ -894,18 +884,33 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
     uint32_t qf[kQuant ? kQTerms * 4 : 8][2];
     float qmul0 = 1.f, qmul1 = 1.f;      // what the 8-bit terms of score columns 2t, 2t+1 must be multiplied by
     if constexpr (!kQuant) {
-      const uint32_t* qrow = reinterpret_cast<const uint32_t*>(
-          reinterpret_cast<const uint16_t*>(p.q) +
-          ((int64_t)s * p.n_q_heads + (int64_t)kvh * G + g) * kHeadDim);
       const bool have = active && g < G;
+      if (q_ll_row) {
+        const unsigned long long t0 = global_ns();
+        for (;;) {
+          bool fresh = true;
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        qf[ks][0] = have ? __ldcg(qrow + ks * 8 + t) : 0u;
-        qf[ks][1] = have ? __ldcg(qrow + ks * 8 + 4 + t) : 0u;
+          for (int ks = 0; ks < 8; ++ks) {
+            const unsigned long long w0 = have ? ld_ll(q_ll_row + ks * 8 + t) : ll_word(0u, (uint32_t)epoch);
+            const unsigned long long w1 = have ? ld_ll(q_ll_row + ks * 8 + 4 + t) : ll_word(0u, (uint32_t)epoch);
+            qf[ks][0] = (uint32_t)w0;
+            qf[ks][1] = (uint32_t)w1;
+            fresh = fresh && (uint32_t)(w0 >> 32) == (uint32_t)epoch && (uint32_t)(w1 >> 32) == (uint32_t)epoch;
+          }
+          if (__all_sync(0xffffffffu, fresh)) break;
+          if (!q_keep_waiting(p, t0, lane, abort_flag)) return;
+        }
+        if (warp == 0 && lane == 0) trace_first(p, 1);
+      } else {
+        const uint32_t* qrow = reinterpret_cast<const uint32_t*>(p.q) + q_row * (kHeadDim / 2);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          qf[ks][0] = have ? __ldcg(qrow + ks * 8 + t) : 0u;
+          qf[ks][1] = have ? __ldcg(qrow + ks * 8 + 4 + t) : 0u;
+        }
       }
     } else {
-      const uint16_t* qrow = reinterpret_cast<const uint16_t*>(p.q) +
-                             ((int64_t)s * p.n_q_heads + (int64_t)kvh * G + g) * kHeadDim;
+      const uint16_t* qrow = reinterpret_cast<const uint16_t*>(p.q) + q_row * kHeadDim;
       const bool have = active && g < G;
       auto widen = [](const uint2& raw, float (&v)[4]) {
         if constexpr (QBF16) {
@@ -919,11 +924,32 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
         }
       };
       uint2 qraw[8];
+      if (q_ll_row) {
+        const unsigned long long t0 = global_ns();
+        for (;;) {
+          bool fresh = true;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int d0 = 32 * (i >> 1) + 16 * (i & 1) + 4 * t;      // two words: d0, d0+1 | d0+2, d0+3
+            unsigned long long w0 = ll_word(0u, (uint32_t)epoch), w1 = w0;
+            if (have) ld_ll_x2(q_ll_row + d0 / 2, w0, w1);
+            qraw[i] = make_uint2((uint32_t)w0, (uint32_t)w1);
+            fresh = fresh && (uint32_t)(w0 >> 32) == (uint32_t)epoch && (uint32_t)(w1 >> 32) == (uint32_t)epoch;
+          }
+          if (__all_sync(0xffffffffu, fresh)) break;
+          if (!q_keep_waiting(p, t0, lane, abort_flag)) return;
+        }
+        if (warp == 0 && lane == 0) trace_first(p, 1);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int d0 = 32 * (i >> 1) + 16 * (i & 1) + 4 * t;
+          qraw[i] = have ? __ldcg(reinterpret_cast<const uint2*>(qrow + d0)) : make_uint2(0u, 0u);
+        }
+      }
       float amax = 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const int d0 = 32 * (i >> 1) + 16 * (i & 1) + 4 * t;
-        qraw[i] = have ? __ldcg(reinterpret_cast<const uint2*>(qrow + d0)) : make_uint2(0u, 0u);
         float v[4];
         widen(qraw[i], v);
 #pragma unroll

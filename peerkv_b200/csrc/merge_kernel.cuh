@@ -10,17 +10,18 @@ namespace pkv {
 struct PublishParams {
   const uint4* q;          // [batch][row16] 16-byte words of q
   int batch, row16;        // sequences; 16-byte words per sequence (Hq * 16)
-  uint4* dst[kMaxWorld];   // peers' q inboxes (P2P mapped), one block per peer
-  uint64_t* tags[kMaxWorld];   // peers' per-sequence q tags
+  unsigned long long* dst[kMaxWorld];   // peers' q inboxes (P2P mapped), one block per peer
   const uint64_t* epoch_base;
   uint64_t epoch_rel;
 };
 
 // The stand-alone q publish (the fused home step does the same in its own prologue).
-// One 1024-thread block per destination peer: all loads first, then the P2P stores, a
-// system fence per thread, one block barrier, and the per-sequence tags.
+// One 1024-thread block per destination peer: each 16-byte word of q goes out as four
+// 8-byte {payload, epoch} words, which need neither a fence nor a flag behind them.
 __global__ void __launch_bounds__(1024) publish_q_kernel(const PublishParams p) {
-  uint4* dst = p.dst[blockIdx.x];
+  unsigned long long* dst = p.dst[blockIdx.x];
+  const uint64_t epoch = (p.epoch_base ? *reinterpret_cast<const volatile uint64_t*>(p.epoch_base) : 0ull) +
+                         p.epoch_rel;
   const int64_t n16 = (int64_t)p.batch * p.row16;
   for (int64_t i0 = 0; i0 < n16; i0 += 4096) {
     uint4 v[4];
@@ -32,14 +33,9 @@ __global__ void __launch_bounds__(1024) publish_q_kernel(const PublishParams p) 
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int64_t i = i0 + threadIdx.x + 1024 * u;
-      if (i < n16) dst[i] = v[u];
+      if (i < n16) st_ll_q16(dst + 4 * i, v[u], (uint32_t)epoch);
     }
   }
-  __threadfence_system();
-  __syncthreads();
-  const uint64_t epoch = (p.epoch_base ? *reinterpret_cast<const volatile uint64_t*>(p.epoch_base) : 0ull) +
-                         p.epoch_rel;
-  for (int b = threadIdx.x; b < p.batch; b += blockDim.x) st_release_sys_u64(p.tags[blockIdx.x] + b, epoch);
 }
 
 // Measurement aid: round-trip time of the two things a step sends over the fabric, with
@@ -48,32 +44,55 @@ __global__ void __launch_bounds__(1024) publish_q_kernel(const PublishParams p) 
 // into the other GPU's inbox and passes a system fence, as a partial return does.  role 0
 // starts, role 1 answers; out[0] = elapsed ns of this side, out[1] = 1 if a wait ran out
 // (every wait is bounded by `timeout_ns`).
-__global__ void __launch_bounds__(32) hop_probe_kernel(int role, int iters, int payload_words, uint4* remote_buf,
+// With `ll` set the bounce is what the query publish does instead: the payload goes out as
+// 8-byte {payload, marker} words (16 bytes per lane and line), no fence and no flag, and the
+// other side polls the words of the last line themselves.  The markers have their top bit
+// set, so that they cannot pass for the epoch of a step.
+__global__ void __launch_bounds__(32) hop_probe_kernel(int role, int ll, int iters, int payload_words,
+                                                       uint4* remote_buf, const uint4* my_buf,
                                                        uint64_t* remote_flag, const uint64_t* my_flag,
                                                        unsigned long long timeout_ns, unsigned long long* out) {
   const int lane = threadIdx.x;
   unsigned long long t0, bad = 0;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-  auto wait_for = [&](uint64_t v) {
-    if (lane == 0) {
-      unsigned long long s, n;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(s));
-      while (ld_acquire_sys_u64(my_flag) < v) {
+  auto wait_for = [&](uint32_t v) {
+    unsigned long long s, n;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(s));
+    if (ll) {
+      const unsigned long long* w = reinterpret_cast<const unsigned long long*>(my_buf + (payload_words - 1) * 32 + lane);
+      for (;;) {
+        unsigned long long a, b;
+        ld_ll_x2(w, a, b);
+        const bool here = (uint32_t)(a >> 32) == (0x80000000u | v) && (uint32_t)(b >> 32) == (0x80000000u | v);
+        if (__all_sync(0xffffffffu, here)) break;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(n));
-        if (n - s > timeout_ns) { bad = 1; break; }
+        if (__any_sync(0xffffffffu, n - s > timeout_ns)) { bad = 1; break; }
       }
+    } else {
+      if (lane == 0) {
+        while (ld_acquire_sys_u64(my_flag) < v) {
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(n));
+          if (n - s > timeout_ns) { bad = 1; break; }
+        }
+      }
+      bad = __shfl_sync(0xffffffffu, bad, 0);
     }
-    bad = __shfl_sync(0xffffffffu, bad, 0);
   };
   for (int i = 1; i <= iters && !bad; ++i) {
-    if (role == 1) { wait_for((uint64_t)i); if (bad) break; }
-    if (payload_words > 0) {
-      for (int w = 0; w < payload_words; ++w) remote_buf[w * 32 + lane] = make_uint4(i, w, lane, 1u);
-      __threadfence_system();
-      __syncwarp();
+    if (role == 1) { wait_for((uint32_t)i); if (bad) break; }
+    if (ll) {
+      for (int w = 0; w < payload_words; ++w)
+        st_ll_x2(reinterpret_cast<unsigned long long*>(remote_buf + w * 32 + lane),
+                 ll_word((uint32_t)w, 0x80000000u | (uint32_t)i), ll_word((uint32_t)lane, 0x80000000u | (uint32_t)i));
+    } else {
+      if (payload_words > 0) {
+        for (int w = 0; w < payload_words; ++w) remote_buf[w * 32 + lane] = make_uint4(i, 0u, lane, 0u);
+        __threadfence_system();
+        __syncwarp();
+      }
+      if (lane == 0) st_release_sys_u64(remote_flag, (uint64_t)i);
     }
-    if (lane == 0) st_release_sys_u64(remote_flag, (uint64_t)i);
-    if (role == 0) wait_for((uint64_t)i);
+    if (role == 0) wait_for((uint32_t)i);
   }
   if (lane == 0) {
     unsigned long long t1;

@@ -173,4 +173,31 @@ __device__ __forceinline__ void st_release_sys_u64(uint64_t* p, uint64_t v) {
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
+
+// "Flag in the data" words for the query rows that cross the fabric: an 8-byte word holds
+// 4 bytes of payload (low half) and the low 32 bits of the step's epoch (high half).  An
+// aligned 8-byte store is a single access, so a reader that sees the epoch sees the payload
+// of the same store: no fence and no separate flag on either side.  Stores and loads are
+// volatile so that they go out to / come from the memory the other GPU writes.
+__device__ __forceinline__ unsigned long long ll_word(uint32_t data, uint32_t tag) {
+  return (unsigned long long)data | ((unsigned long long)tag << 32);
+}
+__device__ __forceinline__ void st_ll_x2(unsigned long long* p, unsigned long long a, unsigned long long b) {
+  asm volatile("st.volatile.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_ll(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void ld_ll_x2(const unsigned long long* p, unsigned long long& a,
+                                         unsigned long long& b) {
+  asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+// One 16-byte word of plain q (four 32-bit pairs) becomes four 8-byte words.
+__device__ __forceinline__ void st_ll_q16(unsigned long long* dst, const uint4& v, uint32_t tag) {
+  st_ll_x2(dst, ll_word(v.x, tag), ll_word(v.y, tag));
+  st_ll_x2(dst + 2, ll_word(v.z, tag), ll_word(v.w, tag));
+}
+
 }  // namespace pkv
