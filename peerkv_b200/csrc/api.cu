@@ -124,7 +124,7 @@ struct pkv_exchange {
   uint64_t base_host = 0;                   // host mirror of the device-resident epoch base
   uint64_t cap_epoch0 = 0, cap_steps = 0;   // graph capture: epoch at its start, steps it holds
   bool capturing = false;
-  size_t off_q = 0, off_o = 0, off_lse = 0, off_tags = 0, off_probe = 0, slab_bytes = 0;
+  size_t off_q = 0, off_o = 0, off_lse = 0, off_probe = 0, slab_bytes = 0;
   size_t o_part_elems = 0, lse_part_elems = 0;
 };
 
@@ -132,15 +132,13 @@ namespace {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-float* slot_o(pkv_exchange* x, int owner_rank, int slot) {
-  return reinterpret_cast<float*>(x->peer_slab[owner_rank] + x->off_o) + (size_t)slot * x->o_part_elems;
+// Partial slot `slot` in rank `owner_rank`'s slab, as 8-byte {fp32, epoch} words:
+// O [max_batch][n_q_heads][128] and lse [max_batch][n_q_heads].
+unsigned long long* slot_o(pkv_exchange* x, int owner_rank, int slot) {
+  return reinterpret_cast<unsigned long long*>(x->peer_slab[owner_rank] + x->off_o) + (size_t)slot * x->o_part_elems;
 }
-float* slot_lse(pkv_exchange* x, int owner_rank, int slot) {
-  return reinterpret_cast<float*>(x->peer_slab[owner_rank] + x->off_lse) + (size_t)slot * x->lse_part_elems;
-}
-// tags of slot `slot` in rank `owner_rank`'s slab: [max_batch][n_q_heads], same stride as lse
-uint64_t* slot_tags(pkv_exchange* x, int owner_rank, int slot) {
-  return reinterpret_cast<uint64_t*>(x->peer_slab[owner_rank] + x->off_tags) + (size_t)slot * x->lse_part_elems;
+unsigned long long* slot_lse(pkv_exchange* x, int owner_rank, int slot) {
+  return reinterpret_cast<unsigned long long*>(x->peer_slab[owner_rank] + x->off_lse) + (size_t)slot * x->lse_part_elems;
 }
 // query inbox of rank `owner_rank`: [max_batch][n_q_heads][64] 8-byte {payload, epoch} words
 unsigned long long* q_inbox(pkv_exchange* x, int owner_rank) {
@@ -268,7 +266,8 @@ struct LaunchOut {
   int out_dtype = PKV_F32;
   float* o_part = nullptr;
   float* lse_part = nullptr;
-  uint64_t* part_tags = nullptr;      // released per (sequence, kv-head) after its rows
+  unsigned long long* o_ll = nullptr;     // the rows as {fp32, epoch} words (a slot of an exchange)
+  unsigned long long* lse_ll = nullptr;
   const unsigned long long* q_ll = nullptr;   // peer: the query inbox ({payload, epoch} words)
   const uint64_t* epoch_base = nullptr;
   uint64_t epoch_rel = 0;
@@ -340,7 +339,8 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   p.epoch_base = lo.epoch_base;
   p.epoch_rel = lo.epoch_rel;
   p.q_timeout_ns = kWaitNs;
-  p.part_tags = lo.part_tags;
+  p.o_ll = lo.o_ll;
+  p.lse_ll = lo.lse_ll;
   p.force_empty = kv.n_pages > 0 ? 0 : 1;
   p.trace = s->trace;
   p.stats = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(s->status) + 64);
@@ -370,8 +370,6 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
     p.mg_lse = slot_lse(x, x->rank, 0);
     p.mg_o_stride = (int64_t)x->o_part_elems;
     p.mg_lse_stride = (int64_t)x->lse_part_elems;
-    p.mg_tags = slot_tags(x, x->rank, 0);
-    p.mg_tag_stride = (int64_t)x->lse_part_elems;
     p.mg_timeout_ns = kWaitNs;
     p.mg_status = x->status;
     for (int r = 0; r < x->world; ++r) {
@@ -787,9 +785,8 @@ int pkv_exchange_create(pkv_exchange** out, int device, int rank, int world, int
   x->lse_part_elems = align_up((size_t)max_batch * n_q_heads, 64);
   x->off_q = 0;
   x->off_o = align_up((size_t)max_batch * n_q_heads * (pkv::kHeadDim / 2) * 8, 256);   // 4 payload bytes per 8-byte word
-  x->off_lse = x->off_o + align_up(world * x->o_part_elems * sizeof(float), 256);
-  x->off_tags = x->off_lse + align_up(world * x->lse_part_elems * sizeof(float), 256);
-  x->off_probe = x->off_tags + align_up(world * x->lse_part_elems * sizeof(uint64_t), 256);   // one flag for pkv_exchange_hop_probe
+  x->off_lse = x->off_o + align_up(world * x->o_part_elems * 8, 256);
+  x->off_probe = x->off_lse + align_up(world * x->lse_part_elems * 8, 256);   // one flag for pkv_exchange_hop_probe
   x->slab_bytes = x->off_probe + 256;
   cudaError_t e = cudaMalloc(&x->slab, x->slab_bytes);
   if (e == cudaSuccess) e = cudaMemset(x->slab, 0, x->slab_bytes);
@@ -969,9 +966,8 @@ int pkv_peer_step(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, int32
     aa.q = x->slab + x->off_q;           // not read: the kernel takes the rows from the inbox words
     lo.q_ll = q_inbox(x, x->rank);
   }
-  lo.o_part = slot_o(x, home_rank, x->rank);
-  lo.lse_part = slot_lse(x, home_rank, x->rank);
-  lo.part_tags = slot_tags(x, home_rank, x->rank);
+  lo.o_ll = slot_o(x, home_rank, x->rank);
+  lo.lse_ll = slot_lse(x, home_rank, x->rank);
   rc = launch_decode(s, &aa, lo, static_cast<cudaStream_t>(stream));
   if (rc) return rc;
   x->epoch += 1;
@@ -983,8 +979,10 @@ int pkv_home_partial(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, vo
   int rc = check_step(x, a);
   if (rc) return rc;
   LaunchOut lo;
-  lo.o_part = slot_o(x, x->rank, x->rank);
-  lo.lse_part = slot_lse(x, x->rank, x->rank);
+  lo.epoch_base = epoch_base_dev(x);          // the step pkv_home_publish_q has begun
+  lo.epoch_rel = x->epoch - x->base_host;
+  lo.o_ll = slot_o(x, x->rank, x->rank);
+  lo.lse_ll = slot_lse(x, x->rank, x->rank);
   return launch_decode(s, a, lo, static_cast<cudaStream_t>(stream));
 }
 
@@ -1022,16 +1020,14 @@ int pkv_home_merge(pkv_exchange* x, int32_t batch, uint32_t wait_mask, void* out
   if (!guard.ok) return fail(PKV_E_CUDA, "cannot select device %d", x->device);
   pkv::MergeParams m;
   memset(&m, 0, sizeof m);
-  m.o_parts = slot_o(x, x->rank, 0);
-  m.lse_parts = slot_lse(x, x->rank, 0);
+  m.o_ll = slot_o(x, x->rank, 0);
+  m.lse_ll = slot_lse(x, x->rank, 0);
   m.o_stride = (int64_t)x->o_part_elems;
   m.lse_stride = (int64_t)x->lse_part_elems;
   m.n_parts = x->world;
   m.rows = batch * x->n_q_heads;
   m.out = out; m.out_dtype = out_dtype; m.lse_out = lse_out;
-  m.tags = slot_tags(x, x->rank, 0);
-  m.tag_stride = (int64_t)x->lse_part_elems;
-  m.wait_mask = wait_mask & ~(1u << x->rank);
+  m.wait_mask = wait_mask | (1u << x->rank);
   m.epoch_base = epoch_base_dev(x);
   m.epoch_rel = x->epoch - x->base_host;
   m.timeout_ns = kWaitNs;

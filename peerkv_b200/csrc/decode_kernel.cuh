@@ -93,8 +93,10 @@ struct DecodeParams {
   void* out;                   // [B][Hq][128] final output, or null
   float* o_part;               // [B][Hq][128] f32 normalised shard partial, or null (may be P2P)
   float* lse_part;             // [B][Hq] natural log, or null (may be P2P)
-  uint64_t* part_tags;         // [B][Hq] or null: after the rows of (sequence, kv-head) are out, the
-                               // tags of that group's q heads are released with the epoch (may be P2P)
+  // peer rank: the rows go to the home GPU as {fp32, epoch} words instead (P2P), [B][Hq][128]
+  // and [B][Hq]; nothing else announces them
+  unsigned long long* o_ll;
+  unsigned long long* lse_ll;
   unsigned int* seq_counter;   // [batch][n_kv_heads], zero between launches
   unsigned int* grp_counter;   // [(CTA groups + batch)][n_kv_heads], zero between launches
   int grp_slot0;               // first slot index of the per-group partials
@@ -109,21 +111,21 @@ struct DecodeParams {
   int pub_n;
   unsigned long long* pub_ll[kMaxWorld];
   // home GPU only -- final merge in the tail: after a (sequence, kv-head) is combined locally
-  // the same warp waits (bounded) for the peers' tags of that pair and folds their rows in.
+  // the same warp re-reads (bounded) the peers' rows of that pair until every word shows
+  // this step's epoch, and folds them in.
   int mg_n;                    // partial slots (ranks); 0 = no merge
   int mg_self;                 // this rank's slot (its own rows never leave the registers)
-  uint32_t mg_wait_mask;       // bit r: wait for rank r's tags
-  const float* mg_o;           // slot r at mg_o + r * mg_o_stride: [B][Hq][128]
-  const float* mg_lse;         // slot r at mg_lse + r * mg_lse_stride: [B][Hq]
-  const uint64_t* mg_tags;     // slot r at mg_tags + r * mg_tag_stride: [B][Hq]
-  int64_t mg_o_stride, mg_lse_stride, mg_tag_stride;
+  uint32_t mg_wait_mask;       // bit r: rank r sends a partial this step
+  const unsigned long long* mg_o;     // slot r at mg_o + r * mg_o_stride: [B][Hq][128] words
+  const unsigned long long* mg_lse;   // slot r at mg_lse + r * mg_lse_stride: [B][Hq] words
+  int64_t mg_o_stride, mg_lse_stride;
   uint64_t mg_timeout_ns;
   uint32_t* mg_status;         // the exchange's status word
   // cumulative counters of the shard: [0] launches, [1] (16-token tile, kv-head) units read; or null
   unsigned long long* stats;
   // measurement aid: [CTAs][kTraceWords] %globaltimer stamps, or null
   //   0 CTA start   1 q published (home) / first q rows seen (peer)   2 last tile consumed
-  //   3 last local combine done   4 last peer tag seen (home)   5 last row written
+  //   3 last local combine done   4 last peer row complete (home)   5 last row written
   unsigned long long* trace;
 };
 
@@ -232,8 +234,14 @@ __device__ __forceinline__ void fold_slot(float& M, float& L, float4& acc, float
 // dependent chain of L2 round trips is what costs, so each step first issues all
 // loads of NS slots x NH heads (statistics and rows, none depending on another and no
 // shuffle in between) and only then does the arithmetic.
+//
+// On the home GPU the peers' shard partials are folded in as well.  They arrive as
+// {fp32, epoch} words: a round of loads is repeated (bounded) until every word of it shows
+// `tag`, the low half of this step's epoch.  Returns false, with the exchange's status bit
+// set, if that did not happen in time; once one wait has run out, later ones of the same
+// launch give up at once.
 template <int NH, int NS>   // heads per pass, slots (or peer parts) loaded per round
-__device__ __forceinline__ void combine_heads(const DecodeParams& p, int b, int qh0, int nh,
+__device__ __forceinline__ bool combine_heads(const DecodeParams& p, uint32_t tag, int b, int qh0, int nh,
                                               int c0, int c1, int lane, int emit_slot = -1) {
   float4 acc[NH];
   float M[NH], L[NH];
@@ -275,28 +283,65 @@ __device__ __forceinline__ void combine_heads(const DecodeParams& p, int b, int 
         if (lane == 0) *reinterpret_cast<float2*>(p.part_ml + row * 2) = make_float2(M[i], L[i]);
       }
     }
-    return;
+    return true;
   }
   // The peers' shard partials are slots too: (m = lse * log2 e, l = 1, o = O normalised).
-  for (int r0 = 0; r0 < p.mg_n; r0 += NS) {
-    float ls[NS][NH];
-    float4 os[NS][NH];
-#pragma unroll
-    for (int jj = 0; jj < NS; ++jj) {
-      const int r = min(r0 + jj, p.mg_n - 1);
-#pragma unroll
-      for (int i = 0; i < NH; ++i) {
-        const int64_t row = (int64_t)b * p.n_q_heads + qh0 + (i < nh ? i : 0);
-        ls[jj][i] = __ldcg(p.mg_lse + r * p.mg_lse_stride + row);
-        os[jj][i] = __ldcg(reinterpret_cast<const float4*>(p.mg_o + r * p.mg_o_stride + row * kHeadDim) + lane);
+  // They are {fp32, epoch} words.  First the cheap poll: the lse words of all awaited rows,
+  // one per lane (the writer stores a row's lse word last).  Then every O word is checked,
+  // and only then are the payload halves loaded, NS ranks x NH heads per round like the
+  // slots above (loading and checking whole words in one go would need twice the registers).
+  if (p.mg_n > 0) {
+    const uint32_t mask = p.mg_wait_mask & ~(1u << p.mg_self);
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+      bool fresh = true;
+      for (int idx = lane; idx < p.mg_n * NH; idx += 32) {
+        const int r = idx / NH, i = idx - r * NH;
+        if (((mask >> r) & 1u) && i < nh)
+          fresh = fresh && (uint32_t)(ld_ll(p.mg_lse + r * p.mg_lse_stride + (int64_t)b * p.n_q_heads + qh0 + i) >> 32) == tag;
       }
+      if (__all_sync(0xffffffffu, fresh)) {
+        for (int r = 0; r < p.mg_n; ++r) {
+          if (!((mask >> r) & 1u)) continue;
+#pragma unroll
+          for (int i = 0; i < NH; ++i)
+            if (i < nh)
+              fresh = ll_row_fresh(p.mg_o + r * p.mg_o_stride + ((int64_t)b * p.n_q_heads + qh0 + i) * kHeadDim, tag, lane) && fresh;
+        }
+        if (__all_sync(0xffffffffu, fresh)) break;
+      }
+      int give_up = 0;
+      if (lane == 0) {
+        if ((*reinterpret_cast<const volatile uint32_t*>(p.mg_status) & kStPartialTimeout) ||
+            global_ns() - t0 > p.mg_timeout_ns) {
+          atomicOr(p.mg_status, kStPartialTimeout);
+          give_up = 1;
+        }
+      }
+      if (__shfl_sync(0xffffffffu, give_up, 0)) return false;
+      __nanosleep(32);
     }
+    if (lane == 0) trace_max(p, 4);
+    for (int r0 = 0; r0 < p.mg_n; r0 += NS) {
+      float ls[NS][NH];
+      float4 os[NS][NH];
 #pragma unroll
-    for (int jj = 0; jj < NS; ++jj) {
-      if (r0 + jj < p.mg_n && r0 + jj != p.mg_self) {
+      for (int jj = 0; jj < NS; ++jj) {
+        const int r = min(r0 + jj, p.mg_n - 1);
 #pragma unroll
-        for (int i = 0; i < NH; ++i)
-          fold_slot(M[i], L[i], acc[i], ls[jj][i] * 1.4426950408889634f, 1.f, os[jj][i]);
+        for (int i = 0; i < NH; ++i) {
+          const int64_t row = (int64_t)b * p.n_q_heads + qh0 + (i < nh ? i : 0);
+          ls[jj][i] = ld_ll_payload(p.mg_lse + r * p.mg_lse_stride + row);
+          os[jj][i] = ld_ll_payload4(p.mg_o + r * p.mg_o_stride + row * kHeadDim + lane * 4);
+        }
+      }
+#pragma unroll
+      for (int jj = 0; jj < NS; ++jj) {
+        if (r0 + jj < p.mg_n && ((mask >> (r0 + jj)) & 1u)) {
+#pragma unroll
+          for (int i = 0; i < NH; ++i)
+            fold_slot(M[i], L[i], acc[i], ls[jj][i] * 1.4426950408889634f, 1.f, os[jj][i]);
+        }
       }
     }
   }
@@ -307,47 +352,30 @@ __device__ __forceinline__ void combine_heads(const DecodeParams& p, int b, int 
       float4 v = acc[i];
       v.x *= inv; v.y *= inv; v.z *= inv; v.w *= inv;
       const int64_t idx = ((int64_t)b * p.n_q_heads + qh0 + i) * kHeadDim + lane * 4;
+      const float lse = L[i] > 0.f ? (M[i] + log2f(L[i])) * 0.6931471805599453f : -INFINITY;
+      const int64_t row = (int64_t)b * p.n_q_heads + qh0 + i;
       if (p.out) store_out4(p.out, p.out_dtype, idx, v);
       if (p.o_part) *reinterpret_cast<float4*>(p.o_part + idx) = v;
-      if (p.lse_part && lane == 0)
-        p.lse_part[(int64_t)b * p.n_q_heads + qh0 + i] =
-            L[i] > 0.f ? (M[i] + log2f(L[i])) * 0.6931471805599453f : -INFINITY;
+      if (p.lse_part && lane == 0) p.lse_part[row] = lse;
+      if (p.o_ll) st_ll_row(p.o_ll + row * kHeadDim, p.lse_ll + row, v, lse, tag, lane);
     }
   }
+  if (lane == 0) trace_max(p, 5);
+  return true;
 }
 
 // LIGHT: the CTA runs two consumer warps per head and has few registers per thread:
 // one head per pass, eight slots per round (the 4x4 form would spill and serialise).
 template <bool LIGHT>
-__device__ __forceinline__ void combine_group(const DecodeParams& p, int b, int qh0, int nq,
+__device__ __forceinline__ bool combine_group(const DecodeParams& p, uint32_t tag, int b, int qh0, int nq,
                                               int c0, int c1, int lane, int emit_slot = -1) {
-  if constexpr (LIGHT) {
-    for (int i = 0; i < nq; ++i) combine_heads<1, 8>(p, b, qh0 + i, 1, c0, c1, lane, emit_slot);
-  } else {
-    for (int i = 0; i < nq; i += 4)
-      combine_heads<4, 4>(p, b, qh0 + i, min(4, nq - i), c0, c1, lane, emit_slot);
-  }
-}
-
-// Bounded wait of one warp for the peers' tags of one row (lane r polls rank r).  Returns
-// false, with the status bit set, if a tag did not reach the epoch in time; once one wait
-// has run out, later waits of the same launch give up at once.
-__device__ __forceinline__ bool wait_peer_tags(const DecodeParams& p, uint64_t epoch, int64_t row,
-                                               int lane) {
   bool ok = true;
-  if (lane < p.mg_n && ((p.mg_wait_mask >> lane) & 1u)) {
-    const uint64_t* tag = p.mg_tags + lane * p.mg_tag_stride + row;
-    const unsigned long long t0 = global_ns();
-    for (;;) {
-      if (ld_acquire_sys_u64(tag) >= epoch) break;
-      if ((*reinterpret_cast<const volatile uint32_t*>(p.mg_status) & kStPartialTimeout) ||
-          global_ns() - t0 > p.mg_timeout_ns) { ok = false; break; }
-      __nanosleep(32);
-    }
-    if (!ok) atomicOr(p.mg_status, kStPartialTimeout);
+  if constexpr (LIGHT) {
+    for (int i = 0; i < nq && ok; ++i) ok = combine_heads<1, 8>(p, tag, b, qh0 + i, 1, c0, c1, lane, emit_slot);
+  } else {
+    for (int i = 0; i < nq && ok; i += 4)
+      ok = combine_heads<4, 4>(p, tag, b, qh0 + i, min(4, nq - i), c0, c1, lane, emit_slot);
   }
-  ok = __all_sync(0xffffffffu, ok);
-  if (lane == 0) trace_max(p, 4);
   return ok;
 }
 
@@ -383,18 +411,6 @@ __device__ __forceinline__ bool wait_q_first_word(const DecodeParams& p, uint64_
     if (__shfl_sync(0xffffffffu, ok, 0)) return true;
     if (!q_keep_waiting(p, t0, lane, abort_flag)) return false;
   }
-}
-
-// After a warp has written the rows of (sequence b, q heads qh0 .. qh0+nq-1): make them
-// visible system-wide, then release the tags of those heads.  One tag of the group proves
-// all of the group's rows (the fence of every lane and the warp barrier come first).
-__device__ __forceinline__ void release_unit(const DecodeParams& p, uint64_t epoch, int b, int qh0,
-                                             int nq, int lane) {
-  if (lane == 0) trace_max(p, 5);
-  if (!p.part_tags) return;
-  __threadfence_system();
-  __syncwarp();
-  if (lane < nq) st_release_sys_u64(p.part_tags + (int64_t)b * p.n_q_heads + qh0 + lane, epoch);
 }
 
 // An on-chip wait ended without its barrier: unless the CTA had already aborted for
@@ -691,12 +707,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
           // a peer's rows land in the home GPU's slot: not before the query of this epoch is
           // here, which is also when the home GPU has finished reading the previous rows
           if (p.q_ll && !wait_q_first_word(p, epoch, b, lane, abort_flag)) return;
-          bool ok = true;
-          if (p.mg_n > 0) ok = wait_peer_tags(p, epoch, (int64_t)b * p.n_q_heads + qh0, lane);
-          if (ok) {
-            combine_group<(WPH > 1)>(p, b, qh0, p.group, 0, -1, lane);
-            release_unit(p, epoch, b, qh0, p.group, lane);
-          }
+          combine_group<(WPH > 1)>(p, (uint32_t)epoch, b, qh0, p.group, 0, -1, lane);
         }
       }
     }
@@ -835,25 +846,18 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
   // What the last CTA of a (sequence, kv-head) does for q heads qh0 .. qh0+nq-1 once the
   // pair's slots lo..hi are complete: the final merge and the rows' way out.
   auto finish_unit = [&](int seq, int qh0, int nq, int lo, int hi) {
-    bool ok = true;
     if (p.mg_n > 0) {
       // Home GPU: the peers' rows of this pair are needed, and they usually arrive later
       // than this.  Fold the pair's own slots into one (unnormalised) slot first, so
-      // that what is left to do once the tags are here is one round of loads.
+      // that what is left to do once the rows are here is one round of loads.
       const int us = p.unit_slot0 + seq;
-      combine_group<(WPH > 1)>(p, seq, qh0, nq, lo, hi, lane, us);
+      combine_group<(WPH > 1)>(p, (uint32_t)epoch, seq, qh0, nq, lo, hi, lane, us);
       __threadfence_block();
       __syncwarp();
       lo = hi = us;
-      if (lane == 0) trace_max(p, 3);
-      ok = wait_peer_tags(p, epoch, (int64_t)seq * p.n_q_heads + qh0, lane);
-    } else if (lane == 0) {
-      trace_max(p, 3);
     }
-    if (ok) {
-      combine_group<(WPH > 1)>(p, seq, qh0, nq, lo, hi, lane);
-      release_unit(p, epoch, seq, qh0, nq, lane);
-    }
+    if (lane == 0) trace_max(p, 3);
+    combine_group<(WPH > 1)>(p, (uint32_t)epoch, seq, qh0, nq, lo, hi, lane);
   };
 
   int s = find_seq(prefix, p.batch, g0);
@@ -1327,7 +1331,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
         }
         glast = __shfl_sync(0xffffffffu, glast, 0);
         if (glast) {
-          combine_group<(WPH > 1)>(p, s, kvh * G, G, cg0 + s, cg1 + s, lane, p.grp_slot0 + gi + s);
+          combine_group<(WPH > 1)>(p, (uint32_t)epoch, s, kvh * G, G, cg0 + s, cg1 + s, lane, p.grp_slot0 + gi + s);
           __threadfence();
           __syncwarp();
           if (lane == 0) {

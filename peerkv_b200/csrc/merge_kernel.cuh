@@ -113,10 +113,11 @@ struct MergeParams {
   void* out;
   int out_dtype;
   float* lse_out;
-  // optional bounded wait, per row: tags[i*tag_stride + row] >= epoch for every part i with
-  // bit i of wait_mask
-  const uint64_t* tags;
-  int64_t tag_stride;
+  // the slots of an exchange instead of o_parts / lse_parts: {fp32, epoch} words, same
+  // strides (in words); the parts with bit i of wait_mask are re-read (bounded) until every
+  // word shows the epoch, the others are left out
+  const unsigned long long* o_ll;
+  const unsigned long long* lse_ll;
   uint32_t wait_mask;
   const uint64_t* epoch_base;
   uint64_t epoch_rel;
@@ -129,27 +130,53 @@ __global__ void __launch_bounds__(256) merge_partials_kernel(const MergeParams p
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + warp;
   if (row >= p.rows) return;
-  if (p.tags && p.wait_mask) {
+  if (p.o_ll) {
     const uint64_t epoch = (p.epoch_base ? *reinterpret_cast<const volatile uint64_t*>(p.epoch_base) : 0ull) +
                            p.epoch_rel;
-    bool ok = true;
-    if (lane < p.n_parts && ((p.wait_mask >> lane) & 1u)) {
-      const uint64_t* tag = p.tags + lane * p.tag_stride + row;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float M = -INFINITY, wsum = 0.f;
+    for (int i = 0; i < p.n_parts; ++i) {
+      if (!((p.wait_mask >> i) & 1u)) continue;
+      float4 v;
+      float li;
       uint64_t t0, now;
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
       for (;;) {
-        if (ld_acquire_sys_u64(tag) >= epoch) break;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-        if ((*reinterpret_cast<const volatile uint32_t*>(p.status) & kStPartialTimeout) ||
-            now - t0 > p.timeout_ns) {
-          atomicOr(p.status, kStPartialTimeout);
-          ok = false;
+        const unsigned long long* o_row = p.o_ll + i * p.o_stride + (int64_t)row * kHeadDim;
+        const unsigned long long lw = ld_ll(p.lse_ll + i * p.lse_stride + row);
+        const bool fresh = (uint32_t)(lw >> 32) == (uint32_t)epoch && ll_row_fresh(o_row, (uint32_t)epoch, lane);
+        if (__all_sync(0xffffffffu, fresh)) {
+          li = __uint_as_float((uint32_t)lw);
+          v = ld_ll_payload4(o_row + lane * 4);
           break;
         }
+        int give_up = 0;
+        if (lane == 0) {
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+          if ((*reinterpret_cast<const volatile uint32_t*>(p.status) & kStPartialTimeout) ||
+              now - t0 > p.timeout_ns) {
+            atomicOr(p.status, kStPartialTimeout);
+            give_up = 1;
+          }
+        }
+        if (__shfl_sync(0xffffffffu, give_up, 0)) return;   // status says why; the row is left untouched
         __nanosleep(32);
       }
+      if (li == -INFINITY) continue;
+      const float mn = fmaxf(M, li);
+      const float ca = __expf(M - mn), cs = __expf(li - mn);
+      acc.x = acc.x * ca + v.x * cs; acc.y = acc.y * ca + v.y * cs;
+      acc.z = acc.z * ca + v.z * cs; acc.w = acc.w * ca + v.w * cs;
+      wsum = wsum * ca + cs;
+      M = mn;
     }
-    if (!__all_sync(0xffffffffu, ok)) return;   // status says why; the row is left untouched
+    if (wsum > 0.f) {
+      const float inv = 1.f / wsum;
+      acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+    }
+    store_out4(p.out, p.out_dtype, (int64_t)row * kHeadDim + lane * 4, acc);
+    if (p.lse_out && lane == 0) p.lse_out[row] = wsum > 0.f ? M + __logf(wsum) : -INFINITY;
+    return;
   }
   float L = -INFINITY;
   for (int i = 0; i < p.n_parts; ++i) L = fmaxf(L, __ldcg(p.lse_parts + i * p.lse_stride + row));

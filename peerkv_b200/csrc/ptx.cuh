@@ -185,6 +185,9 @@ __device__ __forceinline__ unsigned long long ll_word(uint32_t data, uint32_t ta
 __device__ __forceinline__ void st_ll_x2(unsigned long long* p, unsigned long long a, unsigned long long b) {
   asm volatile("st.volatile.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
 }
+__device__ __forceinline__ void st_ll(unsigned long long* p, unsigned long long a) {
+  asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p), "l"(a) : "memory");
+}
 __device__ __forceinline__ unsigned long long ld_ll(const unsigned long long* p) {
   unsigned long long v;
   asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
@@ -198,6 +201,32 @@ __device__ __forceinline__ void ld_ll_x2(const unsigned long long* p, unsigned l
 __device__ __forceinline__ void st_ll_q16(unsigned long long* dst, const uint4& v, uint32_t tag) {
   st_ll_x2(dst, ll_word(v.x, tag), ll_word(v.y, tag));
   st_ll_x2(dst + 2, ll_word(v.z, tag), ll_word(v.w, tag));
+}
+
+// One row of a shard partial on its way to the home GPU: 128 {fp32, epoch} words of O
+// (lane l holds dims 4l..4l+3) and one of lse, again with nothing behind them.
+__device__ __forceinline__ void st_ll_row(unsigned long long* o_row, unsigned long long* lse_word,
+                                          const float4& v, float lse, uint32_t tag, int lane) {
+  st_ll_x2(o_row + lane * 4, ll_word(__float_as_uint(v.x), tag), ll_word(__float_as_uint(v.y), tag));
+  st_ll_x2(o_row + lane * 4 + 2, ll_word(__float_as_uint(v.z), tag), ll_word(__float_as_uint(v.w), tag));
+  if (lane == 0) st_ll(lse_word, ll_word(__float_as_uint(lse), tag));
+}
+// Whether this lane's four O words of such a row are of step `tag`.
+__device__ __forceinline__ bool ll_row_fresh(const unsigned long long* o_row, uint32_t tag, int lane) {
+  unsigned long long a, b, c, d;
+  ld_ll_x2(o_row + lane * 4, a, b);
+  ld_ll_x2(o_row + lane * 4 + 2, c, d);
+  return (uint32_t)(a >> 32) == tag && (uint32_t)(b >> 32) == tag && (uint32_t)(c >> 32) == tag &&
+         (uint32_t)(d >> 32) == tag;
+}
+// The payload half of a word that an earlier 8-byte load of this thread has found fresh.
+__device__ __forceinline__ float ld_ll_payload(const unsigned long long* w) {
+  uint32_t v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(w) : "memory");
+  return __uint_as_float(v);
+}
+__device__ __forceinline__ float4 ld_ll_payload4(const unsigned long long* w) {
+  return make_float4(ld_ll_payload(w), ld_ll_payload(w + 1), ld_ll_payload(w + 2), ld_ll_payload(w + 3));
 }
 
 }  // namespace pkv
