@@ -724,6 +724,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
     const int ring = warp - kConsumerWarps;
     const CUtensorMap* map = ring ? &tm_v : &tm_k;
     if (lane == 0) prefetch_tensormap(map);
+    const uint64_t stream_policy = l2_policy_evict_first();
     // 16-bit pools: lane -> (head, half of D), 16 lanes, a [64 d][16 tok] box each.
     // 1-byte pools: lane -> head, 8 lanes, a [128 d][16 tok] box each (also 2 KiB), and
     // lanes 8.. copy the tile's fp16 scales.
@@ -780,8 +781,8 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
             if (dh == 0) mbar_arrive_expect_tx(bar, L::kHeadBytes);
             __syncwarp(box_lanes);
             const uint32_t dst = ring_base + stage * L::kSlotBytes + dst_off;
-            if (p.head_major) tma_load_4d(dst, map, bar, dh * 64, tok0, head0 + hh, page);
-            else              tma_load_4d(dst, map, bar, dh * 64, head0 + hh, tok0, page);
+            if (p.head_major) tma_load_4d(dst, map, bar, dh * 64, tok0, head0 + hh, page, stream_policy);
+            else              tma_load_4d(dst, map, bar, dh * 64, head0 + hh, tok0, page, stream_policy);
           }
           if constexpr (kQuant) {
             // scales of the tile: dense [page][tok][head] fp16
@@ -792,13 +793,13 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
               if (lane == 8) {
                 const uint32_t bytes = kTileTok * p.n_kv_heads * 2;
                 mbar_arrive_expect_tx(sbar, bytes);
-                bulk_load(sdst, scale_base + row0 * 2, bytes, sbar);
+                bulk_load(sdst, scale_base + row0 * 2, bytes, sbar, stream_policy);
               }
             } else if (lane >= 8 && lane < 8 + kTileTok) {
               if (lane == 8) mbar_arrive_expect_tx(sbar, kTileTok * 16);
               __syncwarp(0x00ffff00u);
               const int r = lane - 8;
-              bulk_load(sdst + r * 16, scale_base + (row0 + (int64_t)r * p.n_kv_heads) * 2, 16, sbar);
+              bulk_load(sdst + r * 16, scale_base + (row0 + (int64_t)r * p.n_kv_heads) * 2, 16, sbar, stream_policy);
             }
           }
         }
