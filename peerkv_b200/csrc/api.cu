@@ -394,16 +394,27 @@ int launch_decode(pkv_shard* s, const pkv_decode_args* a, const LaunchOut& lo, c
   dim3 grid(n_cta_x, n_hb);
   const dim3 block(pkv::cta_threads(is_quant(kv.dtype) ? kWphQ : 1));
   const bool qbf = a->q_dtype == PKV_BF16;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = is_quant(kv.dtype) ? L8::kTotal : L16::kTotal;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see griddepcontrol.wait in the kernel
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
   switch (kv.dtype) {
-    case PKV_BF16: pkv::decode_partial_kernel<pkv::kKvBF16, true, kStages, 1><<<grid, block, L16::kTotal, st>>>(tk, tv, p); break;
-    case PKV_F16: pkv::decode_partial_kernel<pkv::kKvF16, false, kStages, 1><<<grid, block, L16::kTotal, st>>>(tk, tv, p); break;
+    case PKV_BF16: PKV_CUDA(cudaLaunchKernelEx(&cfg, pkv::decode_partial_kernel<pkv::kKvBF16, true, kStages, 1>, tk, tv, p)); break;
+    case PKV_F16: PKV_CUDA(cudaLaunchKernelEx(&cfg, pkv::decode_partial_kernel<pkv::kKvF16, false, kStages, 1>, tk, tv, p)); break;
     case PKV_INT8:
-      if (qbf) pkv::decode_partial_kernel<pkv::kKvInt8, true, kStagesQ, kWphQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
-      else     pkv::decode_partial_kernel<pkv::kKvInt8, false, kStagesQ, kWphQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
+      if (qbf) PKV_CUDA(cudaLaunchKernelEx(&cfg, pkv::decode_partial_kernel<pkv::kKvInt8, true, kStagesQ, kWphQ>, tk, tv, p));
+      else     PKV_CUDA(cudaLaunchKernelEx(&cfg, pkv::decode_partial_kernel<pkv::kKvInt8, false, kStagesQ, kWphQ>, tk, tv, p));
       break;
     default:
-      if (qbf) pkv::decode_partial_kernel<pkv::kKvFp8, true, kStagesQ, kWphQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
-      else     pkv::decode_partial_kernel<pkv::kKvFp8, false, kStagesQ, kWphQ><<<grid, block, L8::kTotal, st>>>(tk, tv, p);
+      if (qbf) PKV_CUDA(cudaLaunchKernelEx(&cfg, pkv::decode_partial_kernel<pkv::kKvFp8, true, kStagesQ, kWphQ>, tk, tv, p));
+      else     PKV_CUDA(cudaLaunchKernelEx(&cfg, pkv::decode_partial_kernel<pkv::kKvFp8, false, kStagesQ, kWphQ>, tk, tv, p));
       break;
   }
   PKV_CUDA(cudaGetLastError());

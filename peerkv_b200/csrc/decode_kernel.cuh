@@ -287,27 +287,55 @@ __device__ __forceinline__ bool combine_heads(const DecodeParams& p, uint32_t ta
   }
   // The peers' shard partials are slots too: (m = lse * log2 e, l = 1, o = O normalised).
   // They are {fp32, epoch} words.  First the cheap poll: the lse words of all awaited rows,
-  // one per lane (the writer stores a row's lse word last).  Then every O word is checked,
-  // and only then are the payload halves loaded, NS ranks x NH heads per round like the
-  // slots above (loading and checking whole words in one go would need twice the registers).
+  // one per lane (the writer stores a row's lse word last).  Then every O word is loaded
+  // whole and checked; the payload halves are loaded separately, NS ranks x NH heads per
+  // round like the slots above (keeping whole words would need twice the registers).  The
+  // first round's payload loads are issued right behind the whole-word loads, before their
+  // verdict is known: a later load of a location never returns an older value than an
+  // earlier one of the same thread, so if the words were fresh the payload is.
   if (p.mg_n > 0) {
     const uint32_t mask = p.mg_wait_mask & ~(1u << p.mg_self);
+    const int64_t row0 = (int64_t)b * p.n_q_heads + qh0;
+    float ls[NS][NH];
+    float4 os[NS][NH];
+    auto load_round = [&](int r0) {
+#pragma unroll
+      for (int jj = 0; jj < NS; ++jj) {
+        const int r = min(r0 + jj, p.mg_n - 1);
+#pragma unroll
+        for (int i = 0; i < NH; ++i) {
+          const int64_t row = row0 + (i < nh ? i : 0);
+          ls[jj][i] = ld_ll_payload(p.mg_lse + r * p.mg_lse_stride + row);
+          os[jj][i] = ld_ll_payload4(p.mg_o + r * p.mg_o_stride + row * kHeadDim + lane * 4);
+        }
+      }
+    };
+    auto fold_round = [&](int r0) {
+#pragma unroll
+      for (int jj = 0; jj < NS; ++jj) {
+        if (r0 + jj < p.mg_n && ((mask >> (r0 + jj)) & 1u)) {
+#pragma unroll
+          for (int i = 0; i < NH; ++i)
+            if (i < nh) fold_slot(M[i], L[i], acc[i], ls[jj][i] * 1.4426950408889634f, 1.f, os[jj][i]);
+        }
+      }
+    };
     const unsigned long long t0 = global_ns();
     for (;;) {
       bool fresh = true;
       for (int idx = lane; idx < p.mg_n * NH; idx += 32) {
         const int r = idx / NH, i = idx - r * NH;
         if (((mask >> r) & 1u) && i < nh)
-          fresh = fresh && (uint32_t)(ld_ll(p.mg_lse + r * p.mg_lse_stride + (int64_t)b * p.n_q_heads + qh0 + i) >> 32) == tag;
+          fresh = fresh && (uint32_t)(ld_ll(p.mg_lse + r * p.mg_lse_stride + row0 + i) >> 32) == tag;
       }
       if (__all_sync(0xffffffffu, fresh)) {
         for (int r = 0; r < p.mg_n; ++r) {
           if (!((mask >> r) & 1u)) continue;
 #pragma unroll
           for (int i = 0; i < NH; ++i)
-            if (i < nh)
-              fresh = ll_row_fresh(p.mg_o + r * p.mg_o_stride + ((int64_t)b * p.n_q_heads + qh0 + i) * kHeadDim, tag, lane) && fresh;
+            if (i < nh) fresh = ll_row_fresh(p.mg_o + r * p.mg_o_stride + (row0 + i) * kHeadDim, tag, lane) && fresh;
         }
+        load_round(0);
         if (__all_sync(0xffffffffu, fresh)) break;
       }
       int give_up = 0;
@@ -322,27 +350,10 @@ __device__ __forceinline__ bool combine_heads(const DecodeParams& p, uint32_t ta
       __nanosleep(32);
     }
     if (lane == 0) trace_max(p, 4);
-    for (int r0 = 0; r0 < p.mg_n; r0 += NS) {
-      float ls[NS][NH];
-      float4 os[NS][NH];
-#pragma unroll
-      for (int jj = 0; jj < NS; ++jj) {
-        const int r = min(r0 + jj, p.mg_n - 1);
-#pragma unroll
-        for (int i = 0; i < NH; ++i) {
-          const int64_t row = (int64_t)b * p.n_q_heads + qh0 + (i < nh ? i : 0);
-          ls[jj][i] = ld_ll_payload(p.mg_lse + r * p.mg_lse_stride + row);
-          os[jj][i] = ld_ll_payload4(p.mg_o + r * p.mg_o_stride + row * kHeadDim + lane * 4);
-        }
-      }
-#pragma unroll
-      for (int jj = 0; jj < NS; ++jj) {
-        if (r0 + jj < p.mg_n && ((mask >> (r0 + jj)) & 1u)) {
-#pragma unroll
-          for (int i = 0; i < NH; ++i)
-            fold_slot(M[i], L[i], acc[i], ls[jj][i] * 1.4426950408889634f, 1.f, os[jj][i]);
-        }
-      }
+    fold_round(0);
+    for (int r0 = NS; r0 < p.mg_n; r0 += NS) {
+      load_round(r0);
+      fold_round(r0);
     }
   }
 #pragma unroll
@@ -632,6 +643,14 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
     for (int h = 0; h < 4 * kHeadsPerCta; ++h) reinterpret_cast<volatile int*>(sgen + L::kSibOff)[h] = 0;
     fence_barrier_init();
   }
+  // The kernel is launched with programmatic stream serialisation: its CTAs may be placed
+  // as soon as the last CTA of the kernel before it in the stream has left, without waiting
+  // for that kernel's memory to drain.  Nothing of global memory is touched above this
+  // line; below it everything the previous kernel wrote is visible.  The kernel does NOT
+  // trigger its own dependents early: CTAs placed on whichever SM frees first land on other
+  // SMs than last time, and the split of the tile list, which learns per CTA index how fast
+  // its SM streams, then balances worse (measured: 5 % slower steps).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const uint64_t epoch = (p.epoch_base ? *reinterpret_cast<const volatile uint64_t*>(p.epoch_base) : 0ull) +
                          p.epoch_rel;
   int* bound = reinterpret_cast<int*>(sgen + L::kBoundOff);
