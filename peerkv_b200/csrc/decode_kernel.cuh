@@ -240,7 +240,7 @@ __device__ __forceinline__ void fold_slot(float& M, float& L, float4& acc, float
 // `tag`, the low half of this step's epoch.  Returns false, with the exchange's status bit
 // set, if that did not happen in time; once one wait has run out, later ones of the same
 // launch give up at once.
-template <int NH, int NS>   // heads per pass, slots (or peer parts) loaded per round
+template <int NH, int NS, int NP>   // heads per pass; slots per round; peer partials per round
 __device__ __forceinline__ bool combine_heads(const DecodeParams& p, uint32_t tag, int b, int qh0, int nh,
                                               int c0, int c1, int lane, int emit_slot = -1) {
   float4 acc[NH];
@@ -252,8 +252,15 @@ __device__ __forceinline__ bool combine_heads(const DecodeParams& p, uint32_t ta
   }
   const float2* ml2 = reinterpret_cast<const float2*>(p.part_ml);
   for (int base = c0; base <= c1; base += NS) {
-    float2 ml[NS][NH];
+    static_assert(NS * NH <= 32, "one lane per (slot, head) statistic");
     float4 os[NS][NH];
+    // the statistics of row (jj, i) are loaded by lane jj * NH + i alone and handed round
+    // afterwards: every lane loading every row's pair would cost 2 * NS * NH registers
+    float2 ml_mine = make_float2(-INFINITY, 0.f);
+    {
+      const int jj = lane / NH, i = lane - jj * NH;
+      if (jj < NS) ml_mine = __ldcg(ml2 + (int64_t)min(base + jj, c1) * p.n_q_heads + qh0 + (i < nh ? i : 0));
+    }
 #pragma unroll
     for (int jj = 0; jj < NS; ++jj) {
       const int c = min(base + jj, c1);           // clamped: a valid row even past the end
@@ -261,15 +268,16 @@ __device__ __forceinline__ bool combine_heads(const DecodeParams& p, uint32_t ta
 #pragma unroll
       for (int i = 0; i < NH; ++i) {
         const int64_t row = row0 + (i < nh ? i : 0);
-        ml[jj][i] = __ldcg(ml2 + row);
         os[jj][i] = __ldcg(reinterpret_cast<const float4*>(p.part_o + row * kHeadDim) + lane);
       }
     }
 #pragma unroll
     for (int jj = 0; jj < NS; ++jj) {
-      if (base + jj <= c1) {
 #pragma unroll
-        for (int i = 0; i < NH; ++i) fold_slot(M[i], L[i], acc[i], ml[jj][i].x, ml[jj][i].y, os[jj][i]);
+      for (int i = 0; i < NH; ++i) {
+        const float m = __shfl_sync(0xffffffffu, ml_mine.x, jj * NH + i);
+        const float l = __shfl_sync(0xffffffffu, ml_mine.y, jj * NH + i);
+        if (base + jj <= c1) fold_slot(M[i], L[i], acc[i], m, l, os[jj][i]);
       }
     }
   }
@@ -288,7 +296,7 @@ __device__ __forceinline__ bool combine_heads(const DecodeParams& p, uint32_t ta
   // The peers' shard partials are slots too: (m = lse * log2 e, l = 1, o = O normalised).
   // They are {fp32, epoch} words.  First the cheap poll: the lse words of all awaited rows,
   // one per lane (the writer stores a row's lse word last).  Then every O word is loaded
-  // whole and checked; the payload halves are loaded separately, NS ranks x NH heads per
+  // whole and checked; the payload halves are loaded separately, NP ranks x NH heads per
   // round like the slots above (keeping whole words would need twice the registers).  The
   // first round's payload loads are issued right behind the whole-word loads, before their
   // verdict is known: a later load of a location never returns an older value than an
@@ -296,11 +304,11 @@ __device__ __forceinline__ bool combine_heads(const DecodeParams& p, uint32_t ta
   if (p.mg_n > 0) {
     const uint32_t mask = p.mg_wait_mask & ~(1u << p.mg_self);
     const int64_t row0 = (int64_t)b * p.n_q_heads + qh0;
-    float ls[NS][NH];
-    float4 os[NS][NH];
+    float ls[NP][NH];
+    float4 os[NP][NH];
     auto load_round = [&](int r0) {
 #pragma unroll
-      for (int jj = 0; jj < NS; ++jj) {
+      for (int jj = 0; jj < NP; ++jj) {
         const int r = min(r0 + jj, p.mg_n - 1);
 #pragma unroll
         for (int i = 0; i < NH; ++i) {
@@ -312,7 +320,7 @@ __device__ __forceinline__ bool combine_heads(const DecodeParams& p, uint32_t ta
     };
     auto fold_round = [&](int r0) {
 #pragma unroll
-      for (int jj = 0; jj < NS; ++jj) {
+      for (int jj = 0; jj < NP; ++jj) {
         if (r0 + jj < p.mg_n && ((mask >> (r0 + jj)) & 1u)) {
 #pragma unroll
           for (int i = 0; i < NH; ++i)
@@ -351,7 +359,7 @@ __device__ __forceinline__ bool combine_heads(const DecodeParams& p, uint32_t ta
     }
     if (lane == 0) trace_max(p, 4);
     fold_round(0);
-    for (int r0 = NS; r0 < p.mg_n; r0 += NS) {
+    for (int r0 = NP; r0 < p.mg_n; r0 += NP) {
       load_round(r0);
       fold_round(r0);
     }
@@ -382,10 +390,10 @@ __device__ __forceinline__ bool combine_group(const DecodeParams& p, uint32_t ta
                                               int c0, int c1, int lane, int emit_slot = -1) {
   bool ok = true;
   if constexpr (LIGHT) {
-    for (int i = 0; i < nq && ok; ++i) ok = combine_heads<1, 8>(p, tag, b, qh0 + i, 1, c0, c1, lane, emit_slot);
+    for (int i = 0; i < nq && ok; ++i) ok = combine_heads<1, 8, 8>(p, tag, b, qh0 + i, 1, c0, c1, lane, emit_slot);
   } else {
     for (int i = 0; i < nq && ok; i += 4)
-      ok = combine_heads<4, 4>(p, tag, b, qh0 + i, min(4, nq - i), c0, c1, lane, emit_slot);
+      ok = combine_heads<4, 6, 4>(p, tag, b, qh0 + i, min(4, nq - i), c0, c1, lane, emit_slot);
   }
   return ok;
 }
