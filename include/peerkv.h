@@ -170,8 +170,8 @@ int pkv_decode_splits_only(pkv_shard* s, const pkv_decode_args* a, void* stream)
 /* Measurement aid: every later launch on the shard records %globaltimer stamps per CTA
  * into buf (device memory of the shard's GPU, 8 x 64-bit words per CTA, room for 1024
  * CTAs, zeroed by the caller before each launch); NULL switches it off.  Words: 0 CTA
- * start, 1 query published (home) / first query tag seen (peer), 2 last tile consumed,
- * 3 last local combine done, 4 last peer tag seen (home), 5 last output row written.
+ * start, 1 query published (home) / first query rows seen (peer), 2 last tile consumed,
+ * 3 last local combine done, 4 last peer row complete (home), 5 last output row written.
  * No counterpart in the reference. */
 int pkv_shard_trace(pkv_shard* s, uint64_t* buf);
 
@@ -274,8 +274,8 @@ int pkv_kv_append(int device, const void* key, const void* value, int64_t kv_tok
 /* ---- several GPUs ------------------------------------------------------- */
 
 /* Mailboxes of one GPU, allocated once: a q inbox of 8-byte {payload, epoch} words, and
- * `world` partial slots ([max_batch, n_q_heads, 128] fp32 O + [max_batch, n_q_heads]
- * lse each) with one epoch tag per (sequence, q head).  rank 0..world-1; the home rank
+ * `world` partial slots ([max_batch, n_q_heads, 128] O + [max_batch, n_q_heads] lse
+ * each, as 8-byte {fp32, epoch} words).  rank 0..world-1; the home rank
  * is the one that owns q and runs the merge.  Replaces the per-call stream/event/scratch
  * set-up of csrc/peer_fused_attn_ext.cu:81-97 and its cudaMemcpyAsync hops
  * (:100-101,120-123).
@@ -287,8 +287,11 @@ int pkv_kv_append(int device, const void* key, const void* value, int64_t kv_tok
  * it needs until they show the epoch, and writes anything into the home GPU's slot only
  * after it has seen the first word of that sequence.
  * A peer stores the (O, lse) rows of a (sequence, kv-head) into its slot on the home GPU
- * and then the tags of that group's q heads; the home GPU merges a pair as soon as every
- * awaited rank's tag for it has arrived.  The home GPU publishes epoch e+1 only after its
+ * in the same word format; the home GPU polls the lse words of a pair, checks every O
+ * word of it, and merges the pair as soon as all of them show the epoch.  The low 32
+ * bits of the epoch repeat after 2^32 steps; a word can only be taken for a newer one
+ * if it was written exactly a multiple of 2^32 steps earlier and never since.
+ * The home GPU publishes epoch e+1 only after its
  * merge of epoch e has ended, so neither the inbox nor a slot is rewritten while it can
  * still be read, also when steps are enqueued back to back without a host
  * synchronisation.  Every step entry point validates, launches, and only then advances
@@ -349,16 +352,15 @@ int pkv_exchange_hop_probe_reset(pkv_exchange* x, void* stream);
 int pkv_home_publish_q(pkv_exchange* x, const void* q, int32_t batch, void* stream);
 /* Peer rank, one step: advances the epoch, waits (bounded, device side, per sequence)
  * for the q of this epoch, computes the shard partial and stores it into the home
- * rank's slot for this rank, releasing the tags of each (sequence, kv-head) as its rows
- * are out.  a->q is ignored unless q_override != 0; with q_override the kernel reads
+ * rank's slot for this rank as {fp32, epoch} words.  a->q is ignored unless q_override != 0; with q_override the kernel reads
  * a->q at once and waits for nothing, so the caller must order the step after the home
  * GPU's previous merge itself. */
 int pkv_peer_step(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, int32_t home_rank,
                   int32_t q_override, void* stream);
 /* Home rank, one whole step in ONE launch: the kernel first stores q into the peers'
  * inboxes, all warps sharing the rows, then streams the home shard; it combines its
- * splits and, pair by pair, waits (bounded, device side) for the tags of the ranks in
- * wait_mask and folds their partials in.  out [batch, n_q_heads, 128] in out_dtype;
+ * splits and, pair by pair, waits (bounded, device side) for the rows of the ranks in
+ * wait_mask and folds them in; a rank without its bit is left out of the merge.  out [batch, n_q_heads, 128] in out_dtype;
  * lse_out may be NULL.  An empty home pool (n_pages 0) is fine.  Same result as
  * pkv_home_publish_q + pkv_home_partial + pkv_home_merge; replaces the host
  * orchestration of csrc/peer_fused_attn_ext.cu:94-135. */
@@ -366,10 +368,10 @@ int pkv_home_step(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, uint3
                   void* out, int32_t out_dtype, float* lse_out, void* stream);
 /* Home rank: its own shard's partial into its own slot (after pkv_home_publish_q). */
 int pkv_home_partial(pkv_exchange* x, pkv_shard* s, const pkv_decode_args* a, void* stream);
-/* Home rank: waits (bounded, device side, per row) for the tags of the ranks in
- * `wait_mask` (bit r = wait for rank r; ranks whose work is ordered before this
- * call by stream order or events need no bit), then merges all `world` slots into
- * out [batch, n_q_heads, 128] of out_dtype.  Replaces the event join + merge2_h of
+/* Home rank: waits (bounded, device side, per row) until the slots of the ranks in
+ * `wait_mask` (bit r = rank r takes part; this rank's own slot always does) show this
+ * step's epoch in every word, then merges them into out [batch, n_q_heads, 128] of
+ * out_dtype.  A rank without its bit is left out.  Replaces the event join + merge2_h of
  * peer_fused_attn_ext.cu:128-131. */
 int pkv_home_merge(pkv_exchange* x, int32_t batch, uint32_t wait_mask, void* out,
                    int32_t out_dtype, float* lse_out, void* stream);

@@ -202,6 +202,107 @@ def test_a_rejected_step_leaves_the_epoch_where_it_was():
     x0.close(); x1.close(); shard.close()
 
 
+def _two_exchanges(B, Hq):
+    from peerkv_b200.group import Exchange
+    dev0, dev1 = torch.device("cuda:0"), torch.device("cuda:1")
+    x0, x1 = Exchange(dev0, 0, 2, B, Hq), Exchange(dev1, 1, 2, B, Hq)
+    x0.attach(x1); x1.attach(x0)
+    return dev0, dev1, x0, x1
+
+
+def _three_call_step(x0, x1, sh0, sh1, q0, a0, a1, out0):
+    """publish, the two shard partials, merge: the long form of pkv_home_step."""
+    import ctypes as C
+    from peerkv_b200 import _lib, ops
+    L = _lib.lib()
+    dev0, dev1 = x0.device, x1.device
+    with torch.cuda.device(dev0):
+        _lib.check(L.pkv_home_publish_q(x0._h, q0.data_ptr(), q0.shape[0], ops._stream(dev0)))
+    with torch.cuda.device(dev1):
+        _lib.check(L.pkv_peer_step(x1._h, sh1._h, C.byref(a1), 0, 0, ops._stream(dev1)))
+    with torch.cuda.device(dev0):
+        _lib.check(L.pkv_home_partial(x0._h, sh0._h, C.byref(a0), ops._stream(dev0)))
+        _lib.check(L.pkv_home_merge(x0._h, q0.shape[0], 0b10, out0.data_ptr(), _lib.PKV_F16, None,
+                                    ops._stream(dev0)))
+
+
+def test_three_call_form_against_the_oracle_two_steps_in_a_row():
+    """pkv_home_publish_q + pkv_peer_step + pkv_home_partial + pkv_home_merge, twice with no
+    synchronisation in between and a new query the second time: both results must be the
+    unsplit attention over the two shards."""
+    from peerkv_b200 import ops
+    B, Hq, Hkv, D, T0, T1 = 3, 32, 8, 128, 400, 272
+    dev0, dev1, x0, x1 = _two_exchanges(B, Hq)
+    g = torch.Generator().manual_seed(21)
+    K = torch.randn(B, Hkv, T0 + T1, D, generator=g).half()
+    V = torch.randn(B, Hkv, T0 + T1, D, generator=g).half()
+    qs = [torch.randn(B, Hq, D, generator=g).half() for _ in range(2)]
+    K0, V0 = K[:, :, :T0].contiguous().to(dev0), V[:, :, :T0].contiguous().to(dev0)
+    K1, V1 = K[:, :, T0:].contiguous().to(dev1), V[:, :, T0:].contiguous().to(dev1)
+    sh0, sh1 = ops.Shard(dev0, B, Hq), ops.Shard(dev1, B, Hq)
+    sl0 = torch.full((B,), T0, dtype=torch.int32, device=dev0)
+    sl1 = torch.full((B,), T1, dtype=torch.int32, device=dev1)
+    q0s = [q.to(dev0) for q in qs]
+    q_unused = torch.zeros(B, Hq, D, dtype=torch.float16, device=dev1)
+    outs = [torch.empty(B, Hq, D, device=dev0, dtype=torch.float16) for _ in range(2)]
+    scale = 1.0 / D ** 0.5
+    for q0, out0 in zip(q0s, outs):
+        a0 = ops.make_args(q0, ops.contiguous_view(K0, V0), None, 1, sl0, scale)
+        a1 = ops.make_args(q_unused, ops.contiguous_view(K1, V1), None, 1, sl1, scale)
+        _three_call_step(x0, x1, sh0, sh1, q0, a0, a1, out0)
+    torch.cuda.synchronize(dev0); torch.cuda.synchronize(dev1)
+    assert x0.status() == 0 and x1.status() == 0 and sh0.status() == 0 and sh1.status() == 0
+    assert x0.epoch() == 2 and x1.epoch() == 2
+    for q, out0 in zip(qs, outs):
+        ref = orc.dense_attention_fp32(q.unsqueeze(2), K, V).squeeze(2)
+        assert close(out0, ref)
+    x0.close(); x1.close(); sh0.close(); sh1.close()
+
+
+def test_hop_probe_both_forms_and_steps_after_it():
+    """The latency probe bounces a flag, a fenced payload and a payload of self-validating
+    words between two GPUs; none of its waits may run out, and what it leaves in the query
+    inbox must not pass for a query afterwards."""
+    from peerkv_b200 import _lib, ops
+    from peerkv_b200.group import PeerGroup
+    devs = [torch.device("cuda:0"), torch.device("cuda:1")]
+    B, Hq, Hkv, D, T = 2, 32, 8, 128, 256
+    grp = PeerGroup(devs, B, Hq)
+    L = _lib.lib()
+    x0, x1 = grp.xchg[0], grp.xchg[1]
+    res = [torch.zeros(2, dtype=torch.int64, device=d) for d in devs]
+    for form, payload in ((0, 0), (0, 1024), (2, 1024)):
+        for x, d in ((x0, devs[0]), (x1, devs[1])):
+            with torch.cuda.device(d):
+                _lib.check(L.pkv_exchange_hop_probe_reset(x._h, ops._stream(d)))
+            torch.cuda.synchronize(d)
+        with torch.cuda.device(devs[1]):      # the answering side first
+            _lib.check(L.pkv_exchange_hop_probe(x1._h, 0, 1 | form, 64, payload, res[1].data_ptr(),
+                                                ops._stream(devs[1])))
+        with torch.cuda.device(devs[0]):
+            _lib.check(L.pkv_exchange_hop_probe(x0._h, 1, 0 | form, 64, payload, res[0].data_ptr(),
+                                                ops._stream(devs[0])))
+        for d in devs:
+            torch.cuda.synchronize(d)
+        for r in res:
+            assert int(r[1]) == 0 and int(r[0]) > 0          # no wait ran out
+        one_way_us = int(res[0][0]) / (2 * 64) / 1e3
+        assert 0.1 < one_way_us < 1000.0
+    with pytest.raises(_lib.PeerKVError):                      # the word form needs a payload
+        _lib.check(L.pkv_exchange_hop_probe(x0._h, 1, 2, 4, 0, res[0].data_ptr(), ops._stream(devs[0])))
+    g = torch.Generator().manual_seed(5)
+    K = torch.randn(B, Hkv, 2 * T, D, generator=g).half()
+    V = torch.randn(B, Hkv, 2 * T, D, generator=g).half()
+    q = torch.randn(B, Hq, D, generator=g).half()
+    shards = [(K[:, :, r * T:(r + 1) * T].contiguous().to(devs[r]), V[:, :, r * T:(r + 1) * T].contiguous().to(devs[r]))
+              for r in range(2)]
+    out = grp.decode_contiguous(q.to(devs[0]), shards)
+    for d in devs:
+        torch.cuda.synchronize(d)
+    grp.raise_on_status()
+    assert close(out, orc.dense_attention_fp32(q.unsqueeze(2), K, V).squeeze(2))
+
+
 @pytest.mark.parametrize("nproc", [2])
 def test_one_process_per_gpu(nproc):
     """torchrun-style launch of tests/dist_worker.py: mailboxes shared through IPC handles."""
