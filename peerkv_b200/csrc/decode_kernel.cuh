@@ -294,41 +294,28 @@ __device__ __forceinline__ bool combine_heads(const DecodeParams& p, uint32_t ta
     return true;
   }
   // The peers' shard partials are slots too: (m = lse * log2 e, l = 1, o = O normalised).
-  // They are {fp32, epoch} words.  First the cheap poll: the lse words of all awaited rows,
-  // one per lane (the writer stores a row's lse word last).  Then every O word is loaded
-  // whole and checked; the payload halves are loaded separately, NP ranks x NH heads per
-  // round like the slots above (keeping whole words would need twice the registers).  The
-  // first round's payload loads are issued right behind the whole-word loads, before their
-  // verdict is known: a later load of a location never returns an older value than an
-  // earlier one of the same thread, so if the words were fresh the payload is.
+  // They are {fp32, epoch} words.  While they are not there yet, only the lse words of the
+  // awaited rows are polled, one per lane (a writer stores a row's lse word last).  Then the
+  // rows are loaded as whole words, NP ranks x NH heads per round, and a round is repeated
+  // (bounded) until every word of it shows the epoch.
   if (p.mg_n > 0) {
+    static_assert(NP * NH <= 32, "one lane per (rank, head) lse word");
     const uint32_t mask = p.mg_wait_mask & ~(1u << p.mg_self);
     const int64_t row0 = (int64_t)b * p.n_q_heads + qh0;
-    float ls[NP][NH];
-    float4 os[NP][NH];
-    auto load_round = [&](int r0) {
-#pragma unroll
-      for (int jj = 0; jj < NP; ++jj) {
-        const int r = min(r0 + jj, p.mg_n - 1);
-#pragma unroll
-        for (int i = 0; i < NH; ++i) {
-          const int64_t row = row0 + (i < nh ? i : 0);
-          ls[jj][i] = ld_ll_payload(p.mg_lse + r * p.mg_lse_stride + row);
-          os[jj][i] = ld_ll_payload4(p.mg_o + r * p.mg_o_stride + row * kHeadDim + lane * 4);
-        }
-      }
-    };
-    auto fold_round = [&](int r0) {
-#pragma unroll
-      for (int jj = 0; jj < NP; ++jj) {
-        if (r0 + jj < p.mg_n && ((mask >> (r0 + jj)) & 1u)) {
-#pragma unroll
-          for (int i = 0; i < NH; ++i)
-            if (i < nh) fold_slot(M[i], L[i], acc[i], ls[jj][i] * 1.4426950408889634f, 1.f, os[jj][i]);
-        }
-      }
-    };
     const unsigned long long t0 = global_ns();
+    auto give_up = [&]() {
+      int stop = 0;
+      if (lane == 0) {
+        if ((*reinterpret_cast<const volatile uint32_t*>(p.mg_status) & kStPartialTimeout) ||
+            global_ns() - t0 > p.mg_timeout_ns) {
+          atomicOr(p.mg_status, kStPartialTimeout);
+          stop = 1;
+        }
+      }
+      stop = __shfl_sync(0xffffffffu, stop, 0);
+      if (!stop) __nanosleep(32);
+      return stop != 0;
+    };
     for (;;) {
       bool fresh = true;
       for (int idx = lane; idx < p.mg_n * NH; idx += 32) {
@@ -336,33 +323,48 @@ __device__ __forceinline__ bool combine_heads(const DecodeParams& p, uint32_t ta
         if (((mask >> r) & 1u) && i < nh)
           fresh = fresh && (uint32_t)(ld_ll(p.mg_lse + r * p.mg_lse_stride + row0 + i) >> 32) == tag;
       }
-      if (__all_sync(0xffffffffu, fresh)) {
-        for (int r = 0; r < p.mg_n; ++r) {
-          if (!((mask >> r) & 1u)) continue;
+      if (__all_sync(0xffffffffu, fresh)) break;
+      if (give_up()) return false;
+    }
+    for (int r0 = 0; r0 < p.mg_n; r0 += NP) {
+      float4 os[NP][NH];
+      float lse_mine = -INFINITY;
+      for (;;) {
+        bool fresh = true;
+        {
+          const int jj = lane / NH, i = lane - jj * NH, r = r0 + jj;
+          if (jj < NP && r < p.mg_n && ((mask >> r) & 1u) && i < nh) {
+            const unsigned long long w = ld_ll(p.mg_lse + r * p.mg_lse_stride + row0 + i);
+            fresh = (uint32_t)(w >> 32) == tag;
+            lse_mine = __uint_as_float((uint32_t)w);
+          }
+        }
 #pragma unroll
-          for (int i = 0; i < NH; ++i)
-            if (i < nh) fresh = ll_row_fresh(p.mg_o + r * p.mg_o_stride + (row0 + i) * kHeadDim, tag, lane) && fresh;
+        for (int jj = 0; jj < NP; ++jj) {
+          const int r = min(r0 + jj, p.mg_n - 1);               // clamped: always a row of the slab
+          const bool use = r0 + jj < p.mg_n && ((mask >> r) & 1u);
+#pragma unroll
+          for (int i = 0; i < NH; ++i) {
+            const bool row_fresh =
+                ld_ll_row4(p.mg_o + r * p.mg_o_stride + (row0 + (i < nh ? i : 0)) * kHeadDim + lane * 4, tag, os[jj][i]);
+            fresh = fresh && (row_fresh || !use || i >= nh);
+          }
         }
-        load_round(0);
         if (__all_sync(0xffffffffu, fresh)) break;
+        if (give_up()) return false;
       }
-      int give_up = 0;
-      if (lane == 0) {
-        if ((*reinterpret_cast<const volatile uint32_t*>(p.mg_status) & kStPartialTimeout) ||
-            global_ns() - t0 > p.mg_timeout_ns) {
-          atomicOr(p.mg_status, kStPartialTimeout);
-          give_up = 1;
+#pragma unroll
+      for (int jj = 0; jj < NP; ++jj) {
+        const int r = r0 + jj;
+        const bool use = r < p.mg_n && ((mask >> r) & 1u);
+#pragma unroll
+        for (int i = 0; i < NH; ++i) {
+          const float ls = __shfl_sync(0xffffffffu, lse_mine, jj * NH + i);
+          if (use && i < nh) fold_slot(M[i], L[i], acc[i], ls * 1.4426950408889634f, 1.f, os[jj][i]);
         }
       }
-      if (__shfl_sync(0xffffffffu, give_up, 0)) return false;
-      __nanosleep(32);
     }
     if (lane == 0) trace_max(p, 4);
-    fold_round(0);
-    for (int r0 = NP; r0 < p.mg_n; r0 += NP) {
-      load_round(r0);
-      fold_round(r0);
-    }
   }
 #pragma unroll
   for (int i = 0; i < NH; ++i) {
@@ -384,16 +386,16 @@ __device__ __forceinline__ bool combine_heads(const DecodeParams& p, uint32_t ta
 }
 
 // LIGHT: the CTA runs two consumer warps per head and has few registers per thread:
-// one head per pass, eight slots per round (the 4x4 form would spill and serialise).
+// one head per pass, eight slots and four peer partials per round (wider forms spill).
 template <bool LIGHT>
 __device__ __forceinline__ bool combine_group(const DecodeParams& p, uint32_t tag, int b, int qh0, int nq,
                                               int c0, int c1, int lane, int emit_slot = -1) {
   bool ok = true;
   if constexpr (LIGHT) {
-    for (int i = 0; i < nq && ok; ++i) ok = combine_heads<1, 8, 8>(p, tag, b, qh0 + i, 1, c0, c1, lane, emit_slot);
+    for (int i = 0; i < nq && ok; ++i) ok = combine_heads<1, 8, 4>(p, tag, b, qh0 + i, 1, c0, c1, lane, emit_slot);
   } else {
     for (int i = 0; i < nq && ok; i += 4)
-      ok = combine_heads<4, 6, 4>(p, tag, b, qh0 + i, min(4, nq - i), c0, c1, lane, emit_slot);
+      ok = combine_heads<4, 6, 3>(p, tag, b, qh0 + i, min(4, nq - i), c0, c1, lane, emit_slot);
   }
   return ok;
 }
@@ -417,12 +419,12 @@ __device__ __forceinline__ bool q_keep_waiting(const DecodeParams& p, unsigned l
   return go != 0;
 }
 
-// Bounded wait of one warp for the first query word of sequence s (peer ranks).  The home
-// GPU publishes the query of step e only after its merge of step e-1 has ended, so from
-// here on this rank's slot on the home GPU may be overwritten.
-__device__ __forceinline__ bool wait_q_first_word(const DecodeParams& p, uint64_t epoch, int s, int lane,
-                                                  volatile int* abort_flag) {
-  const unsigned long long* w = p.q_ll + (int64_t)s * p.n_q_heads * (kHeadDim / 2);
+// Bounded wait of one warp (lane 0 polls) until query word `w` shows this step's epoch
+// (peer ranks).  The home GPU publishes the query of step e only after its merge of step e-1
+// has ended, so once any word of a sequence is fresh this rank's slot on the home GPU may
+// be overwritten.
+__device__ __forceinline__ bool wait_q_word(const DecodeParams& p, uint64_t epoch, const unsigned long long* w,
+                                            int lane, volatile int* abort_flag) {
   const unsigned long long t0 = global_ns();
   for (;;) {
     int ok = 1;
@@ -733,7 +735,8 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
           const int qh0 = (head0 + h) * p.group;
           // a peer's rows land in the home GPU's slot: not before the query of this epoch is
           // here, which is also when the home GPU has finished reading the previous rows
-          if (p.q_ll && !wait_q_first_word(p, epoch, b, lane, abort_flag)) return;
+          if (p.q_ll && !wait_q_word(p, epoch, p.q_ll + (int64_t)b * p.n_q_heads * (kHeadDim / 2), lane, abort_flag))
+            return;
           combine_group<(WPH > 1)>(p, (uint32_t)epoch, b, qh0, p.group, 0, -1, lane);
         }
       }
@@ -898,6 +901,12 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k,
     // words: the loads below are repeated (bounded) until every word carries this epoch.
     const int64_t q_row = (int64_t)s * p.n_q_heads + (int64_t)kvh * G + g;
     const unsigned long long* q_ll_row = p.q_ll ? p.q_ll + q_row * (kHeadDim / 2) : nullptr;
+    // A peer's kernel usually starts before the home GPU's: until the query is there, one
+    // lane polls one word of this kv-head's rows (a thousand warps re-reading whole rows
+    // would load the very L2 lines the query is being written to).
+    if (p.q_ll &&
+        !wait_q_word(p, epoch, p.q_ll + ((int64_t)s * p.n_q_heads + (int64_t)kvh * G) * (kHeadDim / 2), lane, abort_flag))
+      return;
 
     // Q^T B-fragments: column n = g is q head kvh*G + g (zero beyond the group).
     // 16-bit pools: k-step ks covers d = 16ks..16ks+15 in the natural order.

@@ -144,10 +144,9 @@ __global__ void __launch_bounds__(256) merge_partials_kernel(const MergeParams p
       for (;;) {
         const unsigned long long* o_row = p.o_ll + i * p.o_stride + (int64_t)row * kHeadDim;
         const unsigned long long lw = ld_ll(p.lse_ll + i * p.lse_stride + row);
-        const bool fresh = (uint32_t)(lw >> 32) == (uint32_t)epoch && ll_row_fresh(o_row, (uint32_t)epoch, lane);
-        if (__all_sync(0xffffffffu, fresh)) {
+        const bool row_fresh = ld_ll_row4(o_row + lane * 4, (uint32_t)epoch, v);
+        if (__all_sync(0xffffffffu, row_fresh && (uint32_t)(lw >> 32) == (uint32_t)epoch)) {
           li = __uint_as_float((uint32_t)lw);
-          v = ld_ll_payload4(o_row + lane * 4);
           break;
         }
         int give_up = 0;

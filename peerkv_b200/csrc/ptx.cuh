@@ -218,22 +218,15 @@ __device__ __forceinline__ void st_ll_row(unsigned long long* o_row, unsigned lo
   st_ll_x2(o_row + lane * 4 + 2, ll_word(__float_as_uint(v.z), tag), ll_word(__float_as_uint(v.w), tag));
   if (lane == 0) st_ll(lse_word, ll_word(__float_as_uint(lse), tag));
 }
-// Whether this lane's four O words of such a row are of step `tag`.
-__device__ __forceinline__ bool ll_row_fresh(const unsigned long long* o_row, uint32_t tag, int lane) {
+// This lane's four O words of such a row (w = row + 4 * lane); false if one is of another step.
+__device__ __forceinline__ bool ld_ll_row4(const unsigned long long* w, uint32_t tag, float4& v) {
   unsigned long long a, b, c, d;
-  ld_ll_x2(o_row + lane * 4, a, b);
-  ld_ll_x2(o_row + lane * 4 + 2, c, d);
+  ld_ll_x2(w, a, b);
+  ld_ll_x2(w + 2, c, d);
+  v = make_float4(__uint_as_float((uint32_t)a), __uint_as_float((uint32_t)b), __uint_as_float((uint32_t)c),
+                  __uint_as_float((uint32_t)d));
   return (uint32_t)(a >> 32) == tag && (uint32_t)(b >> 32) == tag && (uint32_t)(c >> 32) == tag &&
          (uint32_t)(d >> 32) == tag;
-}
-// The payload half of a word that an earlier 8-byte load of this thread has found fresh.
-__device__ __forceinline__ float ld_ll_payload(const unsigned long long* w) {
-  uint32_t v;
-  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(w) : "memory");
-  return __uint_as_float(v);
-}
-__device__ __forceinline__ float4 ld_ll_payload4(const unsigned long long* w) {
-  return make_float4(ld_ll_payload(w), ld_ll_payload(w + 1), ld_ll_payload(w + 2), ld_ll_payload(w + 3));
 }
 
 }  // namespace pkv
