@@ -1,8 +1,8 @@
 """One process per GPU (torchrun): the same step as group.PeerGroup, with the
 mailboxes shared across processes through CUDA IPC handles that travel over
 torch.distributed once, at set-up.  After that no collective runs on the data
-path: q is pushed and partials are gathered with P2P stores and epoch flags by
-the library's own kernels.
+path: q is pushed and partials are gathered with P2P stores of epoch-carrying
+words by the library's own kernels.
 
 Every rank calls `step(...)` once per decode step, in lockstep: rank `home`
 publishes q, computes its own partial and merges; the others compute theirs and
@@ -78,7 +78,7 @@ class DistPeerGroup:
 
     def resync(self):
         """After an error on any rank: all ranks agree on the largest epoch reached, so the
-        next step's tags mean the same thing everywhere (a collective; call it on every rank)."""
+        next step's epoch words mean the same thing everywhere (a collective; call it on every rank)."""
         t = torch.tensor([self.xchg.epoch()], dtype=torch.int64, device=self.device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.pg)
         self.xchg.resync(int(t.item()))

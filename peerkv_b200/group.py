@@ -6,10 +6,10 @@ created once and mapped into each other with peer access.  A step is:
 
     peers: one kernel each -- wait for q, partial over    pkv_peer_step
            their shard, push it into the home GPU's slot
-           (P2P stores + flag)
-    home:  push q to the peers (P2P stores + flag), then  pkv_home_step
-           one kernel -- partial over its own shard, wait
-           for the peers' flags, merge
+           (P2P stores of words that carry the step's epoch)
+    home:  one kernel -- push q to the peers the same     pkv_home_step
+           way, partial over its own shard, wait for the
+           peers' rows, merge
 
 No stream, event or scratch is created per call and the host never blocks.
 Calls on one group must come from one thread and, per GPU, one stream.
@@ -27,7 +27,7 @@ from ._lib import PeerKVError, check
 
 
 class Exchange:
-    """One GPU's mailboxes (q inbox, one partial slot per rank, epoch flags)."""
+    """One GPU's mailboxes (q inbox, one partial slot per rank; every word carries its epoch)."""
 
     def __init__(self, device, rank: int, world: int, max_batch: int, n_q_heads: int):
         self.device = torch.device(device)
