@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(1024) publish_q_kernel(const PublishParams p) 
 // With `ll` set the bounce is what the query publish does instead: the payload goes out as
 // 8-byte {payload, marker} words (16 bytes per lane and line), no fence and no flag, and the
 // other side polls the words of the last line themselves.  The markers have their top bit
-// set, so that they cannot pass for the epoch of a step.
+// set, so that none of them passes for the epoch of one of an exchange's first 2^31 steps.
 __global__ void __launch_bounds__(32) hop_probe_kernel(int role, int ll, int iters, int payload_words,
                                                        uint4* remote_buf, const uint4* my_buf,
                                                        uint64_t* remote_flag, const uint64_t* my_flag,
