@@ -1,5 +1,5 @@
 // Cross-GPU exchange kernels: q publish (home -> peers, P2P stores), the single-pass
-// N-way LSE merge (with a bounded wait on the peers' per-row epoch tags) and the KV
+// N-way LSE merge (on the slots of an exchange: bounded re-reading of {fp32, epoch} words) and the KV
 // quantiser.  Replaces merge2_h (PeerKV csrc/peer_attn_kernels.cuh:64-73) and the
 // cudaMemcpyAsync + event fork/join of csrc/peer_fused_attn_ext.cu:100-102,112-128.
 #pragma once
